@@ -1,0 +1,105 @@
+/* C ABI of libjatai_b200.so: the integer-only (INT8 mantissa + block exponent) training kernels for B200.
+ *
+ * This is the drop-in boundary.  Every entry point below that cites `jatai_cuda.cu:<line>` has the name,
+ * argument order, argument meaning and return convention of the `extern "C"` function at that line of the
+ * reference's jatai_cuda/jatai_cuda.cu, which the reference binds with ctypes (jatai_cuda/ops.py:299-324):
+ * a launcher written for the reference library works on this one after changing the path it dlopens.
+ *
+ * Conventions (jatai_cuda.cu:1051-1059, ops.py:313-324):
+ *   - pointers are raw device pointers (NULL for an absent tensor); dimensions are C ints; block counts are
+ *     long long; the LAST argument of every operation is the launch id `kid`, echoed in the error record;
+ *   - the return value is the cudaError_t of the launch as an int: 0 = launched; invalid arguments return
+ *     cudaErrorInvalidValue (1) and launch nothing;
+ *   - all launches go to the stream given to jt_stream (NULL = legacy default stream); nothing synchronises
+ *     except jt_erro_le and jt_sincroniza, so a whole step can be captured in a CUDA graph;
+ *   - the library allocates no device memory; every input and output is owned by the caller;
+ *   - kernels never trap: a broken invariant is recorded in the device error record and the kernel goes on.
+ *
+ * Tensor formats (jatai_cuda.cu:3-9):
+ *   block tensor: m int8 [R x C] row-major, E int8 [R x C/BLK]; value = m * 2^E; an all-zero block has E = -127;
+ *   raw tensor:   acc int32 [R x C], e int16 [R x C] (one exponent per element).
+ * BLK is 32 by default (jt_blk); 128 is the reference's format.
+ */
+#ifndef JATAI_B200_H
+#define JATAI_B200_H
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- device error record and control --------------------------------------------------------------- */
+/* out[0..5] = n events, code, kid, flat index into the output, value, extra.  Returns n, or -cudaError.
+ * Synchronises.  Codes 1..6 as in the reference (jatai_cuda.cu:22), 7 = a bounded in-kernel wait expired.
+ * jatai_cuda.cu:1062 */
+int jt_erro_le(long long* out);
+int jt_erro_limpa(void);                                   /* jatai_cuda.cu:1069 */
+int jt_sincroniza(void);                                   /* jatai_cuda.cu:1073 */
+void jt_stream(void* cuda_stream);                         /* jatai_cuda.cu:1088 */
+void jt_gemm_split(int alvo_ctas);                         /* jatai_cuda.cu:1089: split-K target (CTAs) of raw GEMMs */
+void jt_gemm_bm(int bm);                                   /* jatai_cuda.cu:1090: accepted, ignored (tile height is fixed) */
+void jt_atencao_linhas(int n);                             /* jatai_cuda.cu:1091: accepted, ignored */
+int jt_res_estocastico(int ligado);                        /* jatai_cuda.cu:1087: only 0 is supported (bit parity) */
+
+/* ---- GEMM: C[M,N] = A[M,K] . B[N,K]^T, operands blocked along K ---------------------------------- */
+/* modo 0 block output (Cm, CE) | 1 raw output (C32, Ce) | 2 block + residual add of X | 3 block h and
+ * Om2/OE2 = relu2(h) | 4 relu2_back(A.B^T, X).  M multiple of 64, N of 128, K of BLK.
+ * jatai_cuda.cu:1093 */
+int jt_gemm_f(const void* A, const void* EA, const void* B, const void* EB, void* Cm, void* CE, void* C32, void* Ce,
+              const void* Xm, const void* XE, void* Om2, void* OE2, int M, int N, int K, int modo, int kid);
+/* jatai_cuda.cu:1124 */
+int jt_gemm(const void* A, const void* EA, const void* B, const void* EB, void* Cm, void* CE, void* C32, void* Ce,
+            int M, int N, int K, int modo, int kid);
+
+/* ---- block operations ---------------------------------------------------------------------------- */
+int jt_quant(const void* acc, const void* e, void* m, void* E, long long nblocos, int kid);                     /* jatai_cuda.cu:1128 */
+int jt_soma(const void* xm, const void* xE, const void* ym, const void* yE, void* zm, void* zE,
+            long long nblocos, int kid);                                                                        /* jatai_cuda.cu:1132 */
+int jt_relu2(const void* hm, const void* hE, void* am, void* aE, long long nblocos, int kid);                   /* jatai_cuda.cu:1137 */
+int jt_relu2_back(const void* gm, const void* gE, const void* hm, const void* hE, void* om, void* oE,
+                  long long nblocos, int kid);                                                                  /* jatai_cuda.cu:1141 */
+int jt_momento(const void* gacc, const void* ge, void* Mm, void* ME, long long nblocos, int kid);               /* jatai_cuda.cu:1146 */
+int jt_peso(void* Wm, void* WE, const void* Mm, const void* ME, void* Rm, void* RE, int k_lr, int ef,
+            long long nblocos, int kid);                                                                        /* jatai_cuda.cu:1150 */
+int jt_transpoe(const void* X, const void* EX, void* Y, void* EY, int R, int C, int kid);                       /* jatai_cuda.cu:1155 */
+int jt_embed(const void* Wm, const void* WE, const void* tok, void* Xm, void* XE, int M, int D, int V, int kid); /* jatai_cuda.cu:1159 */
+int jt_um_quente(const void* tok, void* U, void* UE, int M, int V, int kid);                                    /* jatai_cuda.cu:1163 */
+int jt_rms(const void* Xm, const void* XE, void* Ym, void* YE, void* cr, void* cemax, int M, int D, int log2D,
+           int G, int kid);                                                                                     /* jatai_cuda.cu:1167 */
+int jt_rms_back(const void* gm, const void* gE, const void* ym, const void* yE, const void* cr, const void* cemax,
+                void* om, void* oE, int M, int D, int log2D, int G, int GB, int kid);                           /* jatai_cuda.cu:1171 */
+/* QKV is one block tensor [Bt*T, 3D] (q | k | v); Oacc/Oe raw [Bt*T, D]; P uint8 [Bt*H][T][T] stored key-major.
+ * Head dimension D/H in {4, 16, 64}; T a multiple of 32, at most 1024.  jatai_cuda.cu:1177 */
+int jt_atencao(const void* qm, const void* qE, void* Oacc, void* Oe, void* P, int Bt, int T, int H, int D, int GA, int kid);
+/* Gacc/Ge raw [Bt*T, 3D] (gq | gk | gv).  jatai_cuda.cu:1182 */
+int jt_atencao_back(const void* gom, const void* goE, const void* qm, const void* qE, const void* P, void* Gacc, void* Ge,
+                    int Bt, int T, int H, int D, int GA, int limite, int kid);
+int jt_softmax_ce(const void* acc, const void* e, const void* alvo, void* gm, void* gE, void* d_alvo, void* soma,
+                  int M, int V, int log2M, int kid);                                                            /* jatai_cuda.cu:1195 */
+
+/* The reference's 16-bit residual stream (opt-in ablation, no int64 specification).  Exported so that a launcher
+ * that looks the symbols up keeps working; each returns cudaErrorNotSupported.  jatai_cuda.cu:1074-1086 */
+int jt_para16(const void* xm, const void* xE, void* zm, void* zE, long long nblocos, int kid);
+int jt_para8(const void* xm, const void* xE, void* ym, void* yE, long long nblocos, int kid);
+int jt_soma16(const void* xm, const void* xE, const void* ym, const void* yE, void* zm, void* zE, long long nblocos, int kid);
+
+/* ---- additions of this library (no counterpart in the reference) --------------------------------- */
+/* Exponent block length used by every later call: 32 (default) or 128 (the reference's compile-time BLK,
+ * jatai_cuda.cu:16).  Host state, like jt_stream. */
+int jt_blk(int blk);
+int jt_blk_atual(void);
+/* GEMM path: 0 automatic | 1 tensor cores with FFMA rounding (block 32; exact while every K-block product stays
+ * below 2^18) | 2 CUDA cores (dp4a) | 3 tensor cores with cvt rounding (what 0 selects when the shape allows). */
+int jt_gemm_via(int via);
+/* jt_gemm_f with optional externally supplied row-maximum exponents RA[M], RB[N] (int8).  A data-parallel rank
+ * passes the maxima over all ranks, so that the int32 partial sums of all ranks share one exponent and their
+ * integer sum equals the single-GPU result (the reference's split-K argument, jatai_cuda.cu:214-216). */
+int jt_gemm_ext(const void* A, const void* EA, const void* B, const void* EB, void* Cm, void* CE, void* C32, void* Ce,
+                const void* Xm, const void* XE, void* Om2, void* OE2, const void* RA, const void* RB,
+                int M, int N, int K, int modo, int kid);
+/* R8[i] = max over the nb block exponents of row i of E (int8 [linhas, nb]): the RA / RB above. */
+int jt_max_linha(const void* E, void* R8, int linhas, int nb, int kid);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,403 @@
+// Bandwidth-bound block kernels: quant, soma, relu2(+back), momento, peso, embed, um_quente, transpoe,
+// rms(+back), softmax_ce.  One pass over HBM each, 128-bit accesses.
+//
+// Work decomposition (all kernels): one thread owns 16 consecutive elements of a row = one 128-bit load of
+// int8 mantissas; GL = BLK/16 neighbouring lanes own one exponent block and reduce with xor-shuffles.
+// Arithmetic: the int64 specification of the reference (jatai_cuda/ops.py, cited per kernel) in int32.
+#pragma once
+#include "comum.cuh"
+
+namespace jt {
+
+#define JT_FIO16                                                                         \
+    const long long t_ = (long long)blockIdx.x * blockDim.x + threadIdx.x;               \
+    const bool ativo = t_ < n16;                                                         \
+    const long long t16 = ativo ? t_ : 0;   /* idle lanes recompute thread 0, store nothing */ \
+    const long long o = t16 * 16;                                                        \
+    const long long w = o / BLK;                                                         \
+    const bool lider = ativo && (t16 % (BLK / 16) == 0);
+
+// raw (acc int32, e int16 per element) -> block.  ops.py:125-126
+template <int BLK>
+__global__ void __launch_bounds__(256) k_quant(const int* __restrict__ acc, const int16_t* __restrict__ e, int8_t* __restrict__ m,
+                                               int8_t* __restrict__ E, long long n16, int kid) {
+    JT_FIO16
+    int v[16], ee[16], q[16];
+    le16_i32(acc + o, v);
+    le16_i16(e + o, ee);
+    const int Eo = quant_geral<16, BLK / 16>(v, ee, q, kid, o);
+    if (ativo) grava16(m + o, q);
+    if (lider) E[w] = (int8_t)Eo;
+}
+
+// z = x + y.  ops.py:128-132: ec = max(xE, yE) - 21; v = rnd(x, ec - xE) + rnd(y, ec - yE); quant(v, ec)
+template <int BLK>
+__global__ void __launch_bounds__(256) k_soma(const int8_t* __restrict__ xm, const int8_t* __restrict__ xE, const int8_t* __restrict__ ym,
+                                              const int8_t* __restrict__ yE, int8_t* __restrict__ zm, int8_t* __restrict__ zE,
+                                              long long n16, int kid) {
+    JT_FIO16
+    int a[16], b[16], v[16], q[16];
+    le16(xm + o, a);
+    le16(ym + o, b);
+    const int ex = xE[w], ey = yE[w], ec = max(ex, ey) - 21;
+    const int sx = ec - ex, sy = ec - ey;          // >= -21: the left shifts stay below 2^28
+#pragma unroll
+    for (int i = 0; i < 16; i++) v[i] = desloca(a[i], sx) + desloca(b[i], sy);
+    const int Eo = quant_uniforme<16, BLK / 16>(v, ec, q, kid, o);
+    if (ativo) grava16(zm + o, q);
+    if (lider) zE[w] = (int8_t)Eo;
+}
+
+// a = max(h, 0)^2.  ops.py:134-137
+template <int BLK>
+__global__ void __launch_bounds__(256) k_relu2(const int8_t* __restrict__ hm, const int8_t* __restrict__ hE, int8_t* __restrict__ am,
+                                               int8_t* __restrict__ aE, long long n16, int kid) {
+    JT_FIO16
+    int h[16], v[16], q[16];
+    le16(hm + o, h);
+#pragma unroll
+    for (int i = 0; i < 16; i++) { const int r = max(h[i], 0); v[i] = r * r; }
+    const int Eo = quant_uniforme<16, BLK / 16>(v, 2 * (int)hE[w], q, kid, o);
+    if (ativo) grava16(am + o, q);
+    if (lider) aE[w] = (int8_t)Eo;
+}
+
+// gh = g * 2 * max(h, 0).  ops.py:139-141
+template <int BLK>
+__global__ void __launch_bounds__(256) k_relu2_back(const int8_t* __restrict__ gm, const int8_t* __restrict__ gE, const int8_t* __restrict__ hm,
+                                                    const int8_t* __restrict__ hE, int8_t* __restrict__ om, int8_t* __restrict__ oE,
+                                                    long long n16, int kid) {
+    JT_FIO16
+    int g[16], h[16], v[16], q[16];
+    le16(gm + o, g);
+    le16(hm + o, h);
+#pragma unroll
+    for (int i = 0; i < 16; i++) v[i] = g[i] * max(h[i], 0) * 2;
+    const int Eo = quant_uniforme<16, BLK / 16>(v, (int)gE[w] + (int)hE[w], q, kid, o);
+    if (ativo) grava16(om + o, q);
+    if (lider) oE[w] = (int8_t)Eo;
+}
+
+// momentum, in place: m <- quant(rnd(7 m, ec - em) + rnd(g, ec - eg), ec), em = ME - 3,
+// per element ec = max(em + 10, eg + bitlen(g)) - 28.  ops.py:273-278
+template <int BLK>
+__global__ void __launch_bounds__(256) k_momento(const int* __restrict__ gacc, const int16_t* __restrict__ ge, int8_t* __restrict__ Mm,
+                                                 int8_t* __restrict__ ME, long long n16, int kid) {
+    JT_FIO16
+    int mm[16], g[16], eg[16], v[16], ee[16], q[16];
+    le16(Mm + o, mm);
+    le16_i32(gacc + o, g);
+    le16_i16(ge + o, eg);
+    const int em = (int)ME[w] - 3;
+#pragma unroll
+    for (int i = 0; i < 16; i++) {
+        if (g[i] >= LIM || g[i] <= -LIM) reporta(E_ACUM, kid, o + i, g[i], eg[i]);
+        const int ec = max(em + 10, eg[i] + bitlen(g[i])) - 28;
+        v[i] = rnd(mm[i] * 7, ec - em, kid, o + i) + rnd(g[i], ec - eg[i], kid, o + i);
+        ee[i] = ec;
+    }
+    const int Eo = quant_geral<16, BLK / 16>(v, ee, q, kid, o);
+    if (ativo) grava16(Mm + o, q);
+    if (lider) ME[w] = (int8_t)Eo;
+}
+
+// weight step with error feedback, in place on W and R.  ops.py:280-290
+template <int BLK>
+__global__ void __launch_bounds__(256) k_peso(int8_t* __restrict__ Wm, int8_t* __restrict__ WE, const int8_t* __restrict__ Mm,
+                                              const int8_t* __restrict__ ME, int8_t* __restrict__ Rm, int8_t* __restrict__ RE, int k_lr, int ef,
+                                              long long n16, int kid) {
+    JT_FIO16
+    int wv[16], mv[16], rv[16], alvo[16], q[16];
+    le16(Wm + o, wv);
+    le16(Mm + o, mv);
+    if (ef) le16(Rm + o, rv);
+    else {
+#pragma unroll
+        for (int i = 0; i < 16; i++) rv[i] = 0;
+    }
+    const int ew = WE[w], em = (int)ME[w] - k_lr, er = ef ? (int)RE[w] : E_ZERO;
+    const int ec = max(max(ew + 7, em + 7), er + 7) - 27;
+#pragma unroll
+    for (int i = 0; i < 16; i++)
+        alvo[i] = rnd(wv[i], ec - ew, kid, o + i) - rnd(mv[i], ec - em, kid, o + i) + (ef ? rnd(rv[i], ec - er, kid, o + i) : 0);
+    const int Ew = quant_uniforme<16, BLK / 16>(alvo, ec, q, kid, o);
+    if (ativo) grava16(Wm + o, q);
+    if (lider) WE[w] = (int8_t)Ew;
+    if (!ef) return;
+    int dif[16], r[16];
+#pragma unroll
+    for (int i = 0; i < 16; i++) dif[i] = alvo[i] - (q[i] == 0 ? 0 : rnd(q[i], ec - Ew, kid, o + i));
+    const int Er = quant_uniforme<16, BLK / 16>(dif, ec, r, kid, o);
+    if (ativo) grava16(Rm + o, r);
+    if (lider) RE[w] = (int8_t)Er;
+}
+
+// row gather of the embedding table; an out-of-range token zeroes the row and records E_ARG.  ops.py:143-145
+template <int BLK>
+__global__ void __launch_bounds__(256) k_embed(const int8_t* __restrict__ Wm, const int8_t* __restrict__ WE, const int* __restrict__ tok,
+                                               int8_t* __restrict__ Xm, int8_t* __restrict__ XE, int M, int D, int V, int kid) {
+    const int por_linha = D / 16;
+    const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= (long long)M * por_linha) return;
+    const int lin = (int)(t / por_linha), c = (int)(t % por_linha) * 16;
+    const int tk = tok[lin];
+    const bool ok = tk >= 0 && tk < V;
+    if (!ok && c == 0) reporta(E_ARG, kid, (long long)lin * D, tk, V);
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (ok) v = *reinterpret_cast<const uint4*>(Wm + (size_t)tk * D + c);
+    *reinterpret_cast<uint4*>(Xm + (size_t)lin * D + c) = v;
+    if (c % BLK == 0) XE[(size_t)lin * (D / BLK) + c / BLK] = ok ? WE[(size_t)tk * (D / BLK) + c / BLK] : (int8_t)E_ZERO;
+}
+
+// one-hot rows with exponent 0 (the embedding gradient is a GEMM on them).  ops.py:147-151
+template <int BLK>
+__global__ void __launch_bounds__(256) k_um_quente(const int* __restrict__ tok, int8_t* __restrict__ U, int8_t* __restrict__ UE, int M, int V,
+                                                   int kid) {
+    const int por_linha = V / 16;
+    const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= (long long)M * por_linha) return;
+    const int lin = (int)(t / por_linha), c = (int)(t % por_linha) * 16;
+    const int tk = tok[lin];
+    if ((tk < 0 || tk >= V) && c == 0) reporta(E_ARG, kid, (long long)lin * V, tk, V);
+    uint32_t u[4] = {0, 0, 0, 0};
+    if (tk >= c && tk < c + 16) u[(tk - c) >> 2] = 1u << (8 * ((tk - c) & 3));
+    *reinterpret_cast<uint4*>(U + (size_t)lin * V + c) = make_uint4(u[0], u[1], u[2], u[3]);
+    if (c % BLK == 0) UE[(size_t)lin * (V / BLK) + c / BLK] = 0;
+}
+
+// [R,C] blocked along C -> [C,R] blocked along R; the new blocks span BLK rows of one column, so every
+// element brings its own exponent and the block is quantised again.  ops.py:121-123
+// Tile: 128 rows x 64 columns through shared memory; a thread then owns 16 consecutive rows of one column.
+template <int BLK>
+__global__ void __launch_bounds__(256) k_transpoe(const int8_t* __restrict__ X, const int8_t* __restrict__ EX, int8_t* __restrict__ Y,
+                                                  int8_t* __restrict__ EY, int R, int C, int kid) {
+    constexpr int TR = 128, TC = 64, NE = (TC + BLK - 1) / BLK;     // exponent columns a tile touches
+    __shared__ int8_t tile[TC][TR + 16];                            // stored transposed: [column][row]
+    __shared__ int8_t et[TR][NE];
+    const int r0 = blockIdx.y * TR, c0 = blockIdx.x * TC;
+    const int tid = threadIdx.x;
+    // load: 128 rows x 64 B = 512 x 16 B, two per thread, scattered transposed into shared memory
+#pragma unroll
+    for (int it = 0; it < 2; it++) {
+        const int idx = tid + it * 256, lr = idx / 4, lc = (idx % 4) * 16;
+        const uint4 v = *reinterpret_cast<const uint4*>(X + (size_t)(r0 + lr) * C + c0 + lc);
+        const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int k = 0; k < 16; k++) tile[lc + k][lr] = (int8_t)(u[k >> 2] >> (8 * (k & 3)));
+    }
+    for (int i = tid; i < TR * NE; i += 256) et[i / NE][i % NE] = EX[(size_t)(r0 + i / NE) * (C / BLK) + c0 / BLK + i % NE];
+    __syncthreads();
+    // 64 columns x 8 row-groups of 16 = 512 tasks; consecutive lanes take consecutive row-groups of a column
+#pragma unroll
+    for (int it = 0; it < 2; it++) {
+        const int idx = tid + it * 256, col = idx / 8, rg = idx % 8;
+        int v[16], e[16], q[16];
+        const uint4 w4 = *reinterpret_cast<const uint4*>(&tile[col][rg * 16]);
+        const uint32_t u[4] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+        for (int k = 0; k < 16; k++) {
+            v[k] = (int)(int8_t)(u[k >> 2] >> (8 * (k & 3)));
+            e[k] = et[rg * 16 + k][(c0 % BLK + col) / BLK];
+        }
+        const long long o = (long long)(c0 + col) * R + r0 + rg * 16;
+        const int Eo = quant_geral<16, BLK / 16>(v, e, q, kid, o);
+        grava16(Y + o, q);
+        if (rg % (BLK / 16) == 0) EY[(size_t)(c0 + col) * (R / BLK) + (r0 + rg * 16) / BLK] = (int8_t)Eo;
+    }
+}
+
+// RMSNorm without gain, one warp per row, NP*512 >= D columns held in registers.  ops.py:153-165
+//   ss = sum_b rnd(sq_b << G, 2 (emax - e_b));  r = isqrt(ss >> log2D);  k = bitlen(r) + 10;  inv = 2^k / r
+//   y = quant(x * inv, e_b - k - emax + G/2);  cache = (r, emax)
+template <int BLK, int NP>
+__global__ void __launch_bounds__(256) k_rms(const int8_t* __restrict__ Xm, const int8_t* __restrict__ XE, int8_t* __restrict__ Ym,
+                                             int8_t* __restrict__ YE, int* __restrict__ cr, int* __restrict__ cemax, int M, int D, int log2D, int G,
+                                             int kid) {
+    constexpr int GL = BLK / 16;
+    const int lane = threadIdx.x & 31;
+    const long long lin_ = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+    const bool linha_ok = lin_ < M;
+    const long long lin = linha_ok ? lin_ : 0;
+    const int nb = D / BLK;
+    int x[NP][16], eb[NP];
+    bool tem[NP];
+    int emax = -128;
+#pragma unroll
+    for (int p = 0; p < NP; p++) {
+        const int c = (p * 32 + lane) * 16;
+        tem[p] = c < D;
+        if (tem[p]) {
+            le16(Xm + lin * D + c, x[p]);
+            eb[p] = XE[lin * nb + c / BLK];
+            emax = max(emax, eb[p]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 16; i++) x[p][i] = 0;
+            eb[p] = E_ZERO;
+        }
+    }
+    emax = warp_max(emax);
+    int ss = 0;
+#pragma unroll
+    for (int p = 0; p < NP; p++) {
+        int sq = 0;
+#pragma unroll
+        for (int i = 0; i < 16; i++) sq += x[p][i] * x[p][i];
+#pragma unroll
+        for (int o = GL / 2; o; o >>= 1) sq += __shfl_xor_sync(FULL, sq, o);      // whole block on every lane of the group
+        if ((lane % GL) == 0 && tem[p]) ss += rnd_d(sq << G, 2 * (emax - eb[p]));
+    }
+    ss = warp_sum(ss);
+    const int r = isqrt_i(ss >> log2D);
+    const int k = bitlen(r) + 10;
+    const int inv = (1 << k) / r;
+#pragma unroll
+    for (int p = 0; p < NP; p++) {
+        int v[16], q[16];
+#pragma unroll
+        for (int i = 0; i < 16; i++) v[i] = x[p][i] * inv;
+        const int c = (p * 32 + lane) * 16;
+        const int Eo = quant_uniforme<16, GL>(v, eb[p] - k - emax + G / 2, q, kid, lin * D + c);
+        if (tem[p] && linha_ok) {
+            grava16(Ym + lin * D + c, q);
+            if ((lane % GL) == 0) YE[lin * nb + c / BLK] = (int8_t)Eo;
+        }
+    }
+    if (lane == 0 && linha_ok) { cr[lin] = r; cemax[lin] = emax; }
+}
+
+// RMSNorm backward: dx = (g - y * mean(g y)) / rms with two shrink steps (15 and 18 bits).  ops.py:167-184
+template <int BLK, int NP>
+__global__ void __launch_bounds__(256) k_rms_back(const int8_t* __restrict__ gm, const int8_t* __restrict__ gE, const int8_t* __restrict__ ym,
+                                                  const int8_t* __restrict__ yE, const int* __restrict__ cr, const int* __restrict__ cemax,
+                                                  int8_t* __restrict__ om, int8_t* __restrict__ oE, int M, int D, int log2D, int G, int GB, int kid) {
+    constexpr int GL = BLK / 16;
+    const int lane = threadIdx.x & 31;
+    const long long lin_ = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+    const bool linha_ok = lin_ < M;
+    const long long lin = linha_ok ? lin_ : 0;
+    const int nb = D / BLK;
+    int g[NP][16], y[NP][16], eg[NP], ey[NP];
+    bool tem[NP];
+    int smax = -100000;
+#pragma unroll
+    for (int p = 0; p < NP; p++) {
+        const int c = (p * 32 + lane) * 16;
+        tem[p] = c < D;
+        if (tem[p]) {
+            le16(gm + lin * D + c, g[p]);
+            le16(ym + lin * D + c, y[p]);
+            eg[p] = gE[lin * nb + c / BLK];
+            ey[p] = yE[lin * nb + c / BLK];
+            smax = max(smax, eg[p] + ey[p]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 16; i++) g[p][i] = y[p][i] = 0;
+            eg[p] = ey[p] = E_ZERO;
+        }
+    }
+    smax = warp_max(smax);
+    int S = 0;
+#pragma unroll
+    for (int p = 0; p < NP; p++) {
+        const int s = smax - (eg[p] + ey[p]);
+#pragma unroll
+        for (int i = 0; i < 16; i++) S += rnd_d((g[p][i] * y[p][i]) << GB, s);
+    }
+    S = warp_sum(S);
+    int eS = smax - GB - log2D;
+    const int sh = max(bitlen(S) - 15, 0);
+    S = rnd_d(S, sh);
+    eS += sh;
+    const int r = cr[lin], emax = cemax[lin];
+    const int k = bitlen(r) + 10;
+    const int inv = (1 << k) / max(r, 1);
+#pragma unroll
+    for (int p = 0; p < NP; p++) {
+        const int c = (p * 32 + lane) * 16;
+        const long long o = lin * D + c;
+        const int ec = max(eg[p] + 7, ey[p] + eS + 22) - 28;
+        int v[16], e[16], q[16];
+#pragma unroll
+        for (int i = 0; i < 16; i++) {
+            int dentro = rnd(g[p][i], ec - eg[p], kid, o + i) - rnd(y[p][i] * S, ec - (ey[p] + eS), kid, o + i);
+            const int sh2 = max(bitlen(dentro) - 18, 0);
+            dentro = rnd_d(dentro, sh2);
+            v[i] = dentro * inv;
+            e[i] = ec + sh2 - k - (emax - G / 2);
+        }
+        const int Eo = quant_geral<16, GL>(v, e, q, kid, o);
+        if (tem[p] && linha_ok) {
+            grava16(om + o, q);
+            if ((lane % GL) == 0) oE[lin * nb + c / BLK] = (int8_t)Eo;
+        }
+    }
+}
+
+// integer softmax + cross-entropy gradient, one warp per row of raw logits.  ops.py:260-271
+//   u = rnd(acc, -(e + 8)); ex = exp(-(umax - u)/256) >> 3; s = sum ex; v = (ex * (2^28 / s) + 2^15) >> 16;
+//   v[target] -= 4096; g = quant(v, -12 - log2M); also d_alvo = umax - u[target] and s for the loss report.
+template <int BLK, int NP>
+__global__ void __launch_bounds__(256) k_softmax_ce(const int* __restrict__ acc, const int16_t* __restrict__ e, const int* __restrict__ alvo,
+                                                    int8_t* __restrict__ gm, int8_t* __restrict__ gE, int* __restrict__ d_alvo, int* __restrict__ soma,
+                                                    int M, int V, int log2M, int kid) {
+    constexpr int GL = BLK / 16;
+    const int lane = threadIdx.x & 31;
+    const long long lin_ = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+    const bool linha_ok = lin_ < M;
+    const long long lin = linha_ok ? lin_ : 0;
+    int u[NP][16];
+    bool tem[NP];
+    int umax = U_MIN;
+    const int tk = alvo[lin];
+    if (lane == 0 && linha_ok && (tk < 0 || tk >= V)) reporta(E_ARG, kid, lin * V, tk, V);
+#pragma unroll
+    for (int p = 0; p < NP; p++) {
+        const int c = (p * 32 + lane) * 16;
+        tem[p] = c < V;
+        if (tem[p]) {
+            int a[16], ee[16];
+            le16_i32(acc + lin * V + c, a);
+            le16_i16(e + lin * V + c, ee);
+#pragma unroll
+            for (int i = 0; i < 16; i++) {
+                u[p][i] = rnd(a[i], -(ee[i] + 8), kid, lin * V + c + i);
+                umax = max(umax, u[p][i]);
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 16; i++) u[p][i] = U_MIN;
+        }
+    }
+    umax = warp_max(umax);
+    int s = 0, ut = U_MIN;
+#pragma unroll
+    for (int p = 0; p < NP; p++) {
+        const int c = (p * 32 + lane) * 16;
+#pragma unroll
+        for (int i = 0; i < 16; i++) {
+            if (c + i == tk) ut = u[p][i];
+            u[p][i] = tem[p] ? exp_dif(umax, u[p][i]) >> 3 : 0;          // u now holds ex
+            s += u[p][i];
+        }
+    }
+    s = warp_sum(s);
+    ut = warp_max(ut);
+    if (s <= 0) { if (lane == 0 && linha_ok) reporta(E_DIV, kid, lin * V, s, 0); s = 1; }
+    const int inv = (1 << 28) / s;
+#pragma unroll
+    for (int p = 0; p < NP; p++) {
+        const int c = (p * 32 + lane) * 16;
+        int v[16], q[16];
+#pragma unroll
+        for (int i = 0; i < 16; i++) v[i] = ((u[p][i] * inv + (1 << 15)) >> 16) - (c + i == tk ? 4096 : 0);
+        const int Eo = quant_uniforme<16, GL>(v, -12 - log2M, q, kid, lin * V + c);
+        if (tem[p] && linha_ok) {
+            grava16(gm + lin * V + c, q);
+            if ((lane % GL) == 0) gE[lin * (V / BLK) + c / BLK] = (int8_t)Eo;
+        }
+    }
+    if (lane == 0 && linha_ok) { d_alvo[lin] = umax - ut; soma[lin] = s; }
+}
+
+}  // namespace jt

@@ -1,0 +1,284 @@
+// Tensor-core block GEMM for sm_100a: tcgen05.mma kind::i8 with the accumulator in tensor memory, operands
+// staged by TMA, and the per-K-block alignment / rounding of the reference specification done on the CUDA
+// cores between the tensor memory and the register accumulators.
+//
+//   C[M,N] = A[M,K] . B[N,K]^T, operands blocked along K (jatai_cuda/ops.py:95-108):
+//   acc_ij = sum over K-blocks b of rnd(p_ijb << 4, (RA_i - ea_ib) + (RB_j - eb_jb)),  p = exact int8 dot product.
+//
+// The rounding of every block's partial product depends on its value, so partial products of different
+// blocks can not be summed by the tensor core.  One MMA instruction of kind::i8 has K = 32: with BLK = 32 every
+// instruction starts a fresh accumulator (tensor-memory stage) that is drained, aligned and added in registers;
+// with BLK = 128 four instructions accumulate in tensor memory before one drain.
+//
+// CTA = one 128 x 128 tile of C (optionally one K range of it: split-K for raw outputs), 10 warps:
+//   warp 0      TMA producer: A and B tiles of 128 rows x 128 bytes of K, SWIZZLE_128B, NST-stage ring
+//   warp 1      allocates tensor memory, issues the MMAs (one thread), frees tensor memory
+//   warps 2..9  drain: thread = one row of the tile (tcgen05.ld 32x32b), 64 columns each, then the output stage
+// Every wait on an mbarrier is bounded: on a timeout the CTA records E_TEMPO, raises an abort flag that turns all
+// later waits into no-ops, and leaves through the normal exit (tensor memory is freed).
+#pragma once
+#include <cuda.h>
+#include "gemm_comum.cuh"
+
+namespace jt {
+namespace tc {
+
+constexpr int TM = 128, KC = 128, NST = 4, NTM = 4, N_EPI = 256, N_THR = 320;
+constexpr uint32_t A_BYTES = TM * KC, B_BYTES = TN * KC, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr uint32_t OFF_ACC = NST * STAGE_BYTES;
+constexpr uint32_t OFF_TAB = OFF_ACC + TM * PITCH * 4;
+constexpr uint32_t OFF_RA = OFF_TAB + 2 * 4 * TN * 4;
+constexpr uint32_t OFF_RB = OFF_RA + TM * 4;
+constexpr uint32_t OFF_BAR = OFF_RB + TN * 4;
+constexpr uint32_t OFF_MISC = OFF_BAR + (2 * NST + 2 * NTM) * 8;
+constexpr uint32_t SMEM_BYTES = OFF_MISC + 16 + 1024;          // + slack to align the base to 1024 bytes
+constexpr long long LIMITE_CICLOS = 4000000000LL;              // ~2 s at B200 clocks
+constexpr uint32_t MAGIA = 0x4B400000u;                        // bit pattern of 1.5 * 2^23
+constexpr float MAGIA_F = 12582912.0f;
+
+// ------------------------------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t n) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(n) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t par) {
+    uint32_t ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(ok) : "r"(bar), "r"(par) : "memory");
+    return ok != 0;
+}
+// bounded wait; false = gave up (abort flag raised by this or another thread)
+__device__ __forceinline__ bool espera(uint32_t bar, uint32_t par, volatile int* aborta, int kid, int onde) {
+    long long t0 = 0;
+    for (int it = 1;; it++) {
+        if (mbar_try(bar, par)) return true;
+        if (*aborta) return false;
+        if ((it & 255) == 0) {
+            const long long agora = clock64();
+            if (t0 == 0) t0 = agora;
+            else if (agora - t0 > LIMITE_CICLOS) {
+                *aborta = 1;
+                reporta(E_TEMPO, kid, onde, par, blockIdx.x + 65536LL * blockIdx.y);
+                return false;
+            }
+        }
+    }
+}
+__device__ __forceinline__ void tma_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_antes() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_depois() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_i8(uint32_t d_tmem, uint64_t da, uint64_t db, uint32_t idesc, uint32_t acumula) {
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+                 " tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n}"
+                 ::"r"(d_tmem), "l"(da), "l"(db), "r"(idesc), "r"(acumula) : "memory");
+}
+// shared-memory matrix descriptor: K-major operand, 128-byte swizzle, 8-row groups 1024 bytes apart
+__device__ __forceinline__ uint64_t desc_sw128(uint32_t addr) {
+    return (uint64_t)((addr >> 4) & 0x3FFF) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// instruction descriptor kind::i8: D = s32, A = B = s8, both K-major, N = 128, M = 128
+constexpr uint32_t IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(TM >> 4) << 24);
+
+#define JT_O4(a, i) "=r"(a[i]), "=r"(a[i + 1]), "=r"(a[i + 2]), "=r"(a[i + 3])
+#define JT_O16(a, i) JT_O4(a, i), JT_O4(a, i + 4), JT_O4(a, i + 8), JT_O4(a, i + 12)
+#define JT_O32(a, i) JT_O16(a, i), JT_O16(a, i + 16)
+// 64 consecutive columns of this thread's tensor-memory lane -> registers; returns when the data has arrived
+__device__ __forceinline__ void tmem_le64(uint32_t taddr, uint32_t (&d)[64]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,"
+        "%24,%25,%26,%27,%28,%29,%30,%31}, [%64];\n"
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%32,%33,%34,%35,%36,%37,%38,%39,%40,%41,%42,%43,%44,%45,%46,%47,%48,%49,%50,%51,%52,%53,"
+        "%54,%55,%56,%57,%58,%59,%60,%61,%62,%63}, [%65];\n"
+        "tcgen05.wait::ld.sync.aligned;\n"
+        : JT_O32(d, 0), JT_O32(d, 32)
+        : "r"(taddr), "r"(taddr + 32)
+        : "memory");
+}
+
+__device__ __forceinline__ float pot2(int e) { return __int_as_float((127 + e) << 23); }      // 2^e, -126 <= e <= 127
+
+// VIA 0: round with one FFMA against 1.5*2^23 and add the bit pattern (valid while |p * 2^(4-s)| < 2^22);
+// VIA 1: exact float product, cvt.rni to int (valid for every input).
+template <int BLK, int MODO, int VIA>
+__global__ void __launch_bounds__(N_THR, 1) k_gemm_tc(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
+                                                      const int8_t* __restrict__ EA, const int8_t* __restrict__ EB,
+                                                      const int8_t* __restrict__ RAg, const int8_t* __restrict__ RBg, SaidaGemm S, int M, int N,
+                                                      int K, int pedacos_por_parte, int kid) {
+    constexpr int NQ = KC / BLK;                 // K-blocks per 128-byte chunk: 4 (BLK 32) or 1 (BLK 128)
+    extern __shared__ unsigned char smem_bruto[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_bruto + 1023) & ~(uintptr_t)1023);
+    const uint32_t sbase = smem_u32(smem);
+    int* acc_s = reinterpret_cast<int*>(smem + OFF_ACC);
+    float* tabB = reinterpret_cast<float*>(smem + OFF_TAB);          // [2][4][TN]
+    int* RAs = reinterpret_cast<int*>(smem + OFF_RA);
+    int* RBs = reinterpret_cast<int*>(smem + OFF_RB);
+    const uint32_t bar_full = sbase + OFF_BAR, bar_empty = bar_full + NST * 8, bar_tfull = bar_empty + NST * 8, bar_tempty = bar_tfull + NTM * 8;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + OFF_MISC);
+    volatile int* aborta = reinterpret_cast<volatile int*>(smem + OFF_MISC + 4);
+
+    const int tid = threadIdx.x, wid = tid >> 5, lane = tid & 31;
+    const int m0 = blockIdx.y * TM, n0 = blockIdx.x * TN;
+    const int nb = K / BLK;
+    const int ped0 = blockIdx.z * pedacos_por_parte;             // first 128-byte chunk of this CTA's K range
+    const int nfatias = pedacos_por_parte * NQ;                  // drains (K-blocks) this CTA performs
+
+    if (tid == 0) {
+        for (int i = 0; i < NST; i++) { mbar_init(bar_full + 8 * i, 1); mbar_init(bar_empty + 8 * i, 1); }
+        for (int i = 0; i < NTM; i++) { mbar_init(bar_tfull + 8 * i, 1); mbar_init(bar_tempty + 8 * i, N_EPI); }
+        *aborta = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (wid == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(NTM * TN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_antes();
+    __syncthreads();
+    tc_fence_depois();
+    const uint32_t tmem = *tmem_slot;
+
+    if (wid == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            for (int i = 0; i < pedacos_por_parte; i++) {
+                const int s = i % NST;
+                if (!espera(bar_empty + 8 * s, ((i / NST) & 1) ^ 1, aborta, kid, 1)) break;
+                mbar_expect_tx(bar_full + 8 * s, STAGE_BYTES);
+                tma_2d(sbase + s * STAGE_BYTES, &mapA, (ped0 + i) * KC, m0, bar_full + 8 * s);
+                tma_2d(sbase + s * STAGE_BYTES + A_BYTES, &mapB, (ped0 + i) * KC, n0, bar_full + 8 * s);
+            }
+        }
+    } else if (wid == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            int f = 0;
+            bool ok = true;
+            for (int i = 0; i < pedacos_por_parte && ok; i++) {
+                const int s = i % NST;
+                if (!espera(bar_full + 8 * s, (i / NST) & 1, aborta, kid, 2)) break;
+                tc_fence_depois();
+                const uint64_t da = desc_sw128(sbase + s * STAGE_BYTES), db = desc_sw128(sbase + s * STAGE_BYTES + A_BYTES);
+                if (BLK == 32) {
+#pragma unroll
+                    for (int q = 0; q < 4; q++, f++) {
+                        const int t = f % NTM;
+                        if (!espera(bar_tempty + 8 * t, ((f / NTM) & 1) ^ 1, aborta, kid, 3)) { ok = false; break; }
+                        tc_fence_depois();
+                        tc_mma_i8(tmem + t * TN, da + 2 * q, db + 2 * q, IDESC, 0);          // +32 bytes of K per instruction
+                        tc_commit(bar_tfull + 8 * t);
+                    }
+                } else {
+                    const int t = f % NTM;
+                    if (!espera(bar_tempty + 8 * t, ((f / NTM) & 1) ^ 1, aborta, kid, 3)) break;
+                    tc_fence_depois();
+#pragma unroll
+                    for (int q = 0; q < 4; q++) tc_mma_i8(tmem + t * TN, da + 2 * q, db + 2 * q, IDESC, q > 0);
+                    tc_commit(bar_tfull + 8 * t);
+                    f++;
+                }
+                tc_commit(bar_empty + 8 * s);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ drain + output stage
+        const int et = tid - 64;                                  // 0..255
+        const int quarto = wid & 3;                               // tensor-memory lanes this warp may read
+        const int metade = (wid - 2) >> 2;                        // column half of the tile
+        const int lin = quarto * 32 + lane;                       // row of the tile = tensor-memory lane
+        if (et < TM) RAs[et] = RAg ? (int)RAg[m0 + et] : max_expoentes(EA + (size_t)(m0 + et) * nb, nb);
+        else RBs[et - TM] = RBg ? (int)RBg[n0 + et - TM] : max_expoentes(EB + (size_t)(n0 + et - TM) * nb, nb);
+        asm volatile("bar.sync 1, %0;" ::"n"(N_EPI) : "memory");
+        const int RA = RAs[lin];
+        const int8_t* ea_lin = EA + (size_t)(m0 + lin) * nb + (size_t)ped0 * NQ;
+        const int8_t* eb_col = EB + (size_t)(n0 + (et & (TN - 1))) * nb + (size_t)ped0 * NQ;
+        const int RBc = RBs[et & (TN - 1)];
+        // exponents of one chunk: NQ bytes per row
+        auto le_exp = [&](const int8_t* p, int c) -> uint32_t {
+            if (NQ == 4) return *reinterpret_cast<const uint32_t*>(p + 4 * c);
+            return (uint32_t)(uint8_t)p[c];
+        };
+        auto grava_tab = [&](int buf, uint32_t w) {
+#pragma unroll
+            for (int q = 0; q < NQ; q++) {
+                const int sb = min(RBc - (int)(int8_t)(w >> (8 * q)), 40);
+                tabB[(buf * 4 + q) * TN + et] = pot2(-sb);
+            }
+        };
+        uint32_t eaw = le_exp(ea_lin, 0), eaw_prox = 0, ebw_prox = 0;
+        if (et < TN) grava_tab(0, le_exp(eb_col, 0));
+        int acc[64];
+#pragma unroll
+        for (int j = 0; j < 64; j++) acc[j] = 0;
+        int f = 0;
+        bool ok = true;
+        for (int c = 0; c < pedacos_por_parte; c++) {
+            // every drain thread passes this barrier once per chunk, aborted or not (no thread may be left waiting)
+            asm volatile("bar.sync 1, %0;" ::"n"(N_EPI) : "memory");
+            if (!ok) continue;
+            if (c + 1 < pedacos_por_parte) {
+                eaw_prox = le_exp(ea_lin, c + 1);
+                if (et < TN) ebw_prox = le_exp(eb_col, c + 1);
+            }
+#pragma unroll 1
+            for (int q = 0; q < NQ; q++, f++) {
+                const int t = f % NTM;
+                ok = espera(bar_tfull + 8 * t, (f / NTM) & 1, aborta, kid, 4);
+                ok = __all_sync(FULL, ok);
+                if (!ok) break;
+                tc_fence_depois();
+                uint32_t d[64];
+                tmem_le64(tmem + ((uint32_t)(quarto * 32) << 16) + t * TN + metade * 64, d);
+                tc_fence_antes();
+                mbar_arrive(bar_tempty + 8 * t);
+                const int sa = min(RA - (int)(int8_t)(eaw >> (8 * q)), 40);
+                const float fa = pot2(GG - sa), cneg = -MAGIA_F * fa;
+                const float4* tb = reinterpret_cast<const float4*>(tabB + ((c & 1) * 4 + q) * TN + metade * 64);
+#pragma unroll
+                for (int j4 = 0; j4 < 16; j4++) {
+                    const float4 fb = tb[j4];
+                    const float fbv[4] = {fb.x, fb.y, fb.z, fb.w};
+#pragma unroll
+                    for (int k = 0; k < 4; k++) {
+                        const int j = j4 * 4 + k;
+                        const float g = fmaf(__int_as_float((int)(d[j] + MAGIA)), fa, cneg);      // = p * 2^(4 - sa), exact
+                        if (VIA == 0) acc[j] += __float_as_int(fmaf(g, fbv[k], MAGIA_F));
+                        else acc[j] += __float2int_rn(g * fbv[k]);
+                    }
+                }
+            }
+            if (ok && c + 1 < pedacos_por_parte && et < TN) grava_tab((c + 1) & 1, ebw_prox);
+            eaw = eaw_prox;
+        }
+        if (VIA == 0) {
+            const uint32_t vies = (uint32_t)nfatias * MAGIA;
+#pragma unroll
+            for (int j = 0; j < 64; j++) acc[j] = (int)((uint32_t)acc[j] - vies);
+        }
+#pragma unroll
+        for (int j = 0; j < 64; j += 4)
+            *reinterpret_cast<int4*>(acc_s + lin * PITCH + metade * 64 + j) = make_int4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+        asm volatile("bar.sync 1, %0;" ::"n"(N_EPI) : "memory");
+        epilogo_tile<BLK, MODO, N_EPI>(acc_s, RAs, RBs, TM, m0, n0, N, S, gridDim.z > 1, blockIdx.z == 0, kid, et);
+    }
+    tc_fence_antes();
+    __syncthreads();
+    if (wid == 1) {
+        tc_fence_depois();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(NTM * TN) : "memory");
+    }
+}
+
+}  // namespace tc
+}  // namespace jt

@@ -1,0 +1,212 @@
+"""Parity of the CUDA kernels with the oracle, through the C ABI (jatai_b200.ops.OpsCuda -> libjatai_b200.so).
+
+Every case of tests/casos.py (the reference's own edge-case list at reduced sizes) runs at block 32 and 128 and
+must equal, bit for bit, (a) the oracle on the same seeded inputs and (b) the committed golden outputs that the
+reference's OpsRef produced.  GEMMs additionally run on each of the three kernel paths.
+"""
+import os
+import tempfile
+
+import pytest
+import torch
+
+import casos
+import golden_util as gu
+from oracle import spec
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+@pytest.fixture(scope="module")
+def amb():
+    from jatai_b200 import ops, registro
+    reg = registro.Registro(tempfile.mkdtemp(), "teste", vigiar=True, eco=False, salvar=False)
+    oc = ops.OpsCuda(reg)
+    reg.novo_passo(0)
+    yield ops, oc, reg
+    ops.define_blk(32)
+    oc.lib.jt_gemm_via(0)
+
+
+def para_gpu(a):
+    if torch.is_tensor(a):
+        return a.to(DEV).contiguous()
+    if isinstance(a, tuple):
+        return tuple(para_gpu(x) for x in a)
+    return a
+
+
+class Adapt:
+    """OpsCuda with the `limite` attribute casos.roda toggles (a module global in the operator module)."""
+
+    def __init__(self, ops, oc):
+        self._ops, self._oc = ops, oc
+
+    def __getattr__(self, n):
+        return getattr(self._oc, n)
+
+    @property
+    def limite(self):
+        return self._ops.ATENCAO_LIMITE
+
+    @limite.setter
+    def limite(self, v):
+        self._ops.ATENCAO_LIMITE = bool(v)
+
+
+def _ids(blk):
+    return [n for n, _, _ in casos.tabela(blk)]
+
+
+def compara(nome, outs, refs):
+    assert len(outs) == len(refs)
+    for i, (a, b) in enumerate(zip(outs, refs)):
+        a, b = a.cpu(), b.cpu()
+        assert a.dtype == b.dtype and a.shape == b.shape, f"{nome} out {i}: {a.dtype}{tuple(a.shape)} vs {b.dtype}{tuple(b.shape)}"
+        dif = a != b
+        if dif.any():
+            p = tuple(dif.nonzero()[0].tolist())
+            raise AssertionError(f"{nome} out {i}: {int(dif.sum())} of {a.numel()} differ; first at {p}: cuda {a[p].item()} oracle {b[p].item()}")
+
+
+@pytest.mark.parametrize("nome,blk,f", casos.tabela(32) + casos.tabela(128), ids=_ids(32) + _ids(128))
+def test_tabela(amb, nome, blk, f):
+    ops, oc, reg = amb
+    ops.define_blk(blk)
+    oc.lib.jt_gemm_via(0)
+    reg.novo_passo(0)
+    G = casos.Gen(casos.semente(nome), blk)
+    op, args, kw = f(G)
+    outs = casos.roda(Adapt(ops, oc), op, tuple(para_gpu(a) for a in args), kw)
+    torch.cuda.synchronize()
+    refs = casos.roda(spec.Spec(blk), op, args, kw)
+    compara(nome, outs, refs)
+    meta, arrs = gu.carrega(blk)
+    gu.confere_saidas(nome, meta[nome], arrs, outs)
+
+
+GEMMS = [(n, b, f) for n, b, f in casos.tabela(32) + casos.tabela(128) if "/gemm" in n]
+
+
+@pytest.mark.parametrize("via", [1, 2, 3])
+@pytest.mark.parametrize("nome,blk,f", GEMMS, ids=[n for n, _, _ in GEMMS])
+def test_gemm_vias(amb, nome, blk, f, via):
+    """via 1 = tensor core with FFMA rounding (block 32 only; not valid for saturated mantissas), 2 = CUDA cores,
+    3 = tensor core with cvt rounding."""
+    ops, oc, reg = amb
+    if via == 1 and (blk != 32 or "limite" in nome):
+        pytest.skip("FFMA rounding is defined for block 32 and partial products below 2^18")
+    ops.define_blk(blk)
+    assert oc.lib.jt_gemm_via(via) == 0
+    try:
+        reg.novo_passo(0)
+        G = casos.Gen(casos.semente(nome), blk)
+        op, args, kw = f(G)
+        outs = casos.roda(oc, op, tuple(para_gpu(a) for a in args), kw)
+        torch.cuda.synchronize()
+        compara(f"{nome} via {via}", outs, casos.roda(spec.Spec(blk), op, args, kw))
+    finally:
+        oc.lib.jt_gemm_via(0)
+
+
+def test_config1(amb):
+    """BASELINE config 1: linear layer forward + both backward GEMMs at block 32, against the reference digests."""
+    import json
+    ops, oc, reg = amb
+    ops.define_blk(32)
+    reg.novo_passo(0)
+    with open(os.path.join(gu.AQUI, "config1_b32.json")) as fh:
+        rec = json.load(fh)
+    X, W, dY = (para_gpu(t) for t in casos.config1(32))
+    Y = oc.gemm(X, W)
+    dX = oc.gemm(dY, oc.transpoe(W))
+    dW = oc.gemm(oc.transpoe(dY), oc.transpoe(X), cru=True)
+    torch.cuda.synchronize()
+    assert [gu.digest(t) for t in Y] == rec["Y"]
+    assert [gu.digest(t) for t in dX] == rec["dX"]
+    assert [gu.digest(t) for t in dW] == rec["dW"]
+
+
+@pytest.mark.parametrize("blk", [32, 128])
+@pytest.mark.parametrize("M,N,K,cru", [(256, 256, 1024, False), (512, 384, 512, True), (128, 128, 4096, True), (1024, 1536, 512, False),
+                                       (64, 128, 256, False), (192, 256, 384, True)])
+def test_gemm_formas(amb, blk, M, N, K, cru):
+    """Shape sweep against the oracle evaluated on the GPU in int64 (includes split-K raw outputs and the
+    shapes only the CUDA-core path takes: M or K not a multiple of 128)."""
+    ops, oc, reg = amb
+    ops.define_blk(blk)
+    reg.novo_passo(0)
+    G = casos.Gen(1000 + M + N + K, blk)
+    A, B = para_gpu(G.bloco(M, K, faixa=(-12, -4))), para_gpu(G.bloco(N, K, espalha=6, zera=0.05))
+    out = oc.gemm(A, B, cru=cru)
+    torch.cuda.synchronize()
+    compara(f"gemm {M}x{N}x{K}", casos.plano(out), casos.plano(spec.Spec(blk).gemm(A, B, cru=cru)))
+
+
+def test_gemm_maximos_externos(amb):
+    """Row maxima supplied by the caller (the data-parallel path): two K halves with the global maxima add up to
+    the full GEMM, bit for bit."""
+    ops, oc, reg = amb
+    ops.define_blk(32)
+    reg.novo_passo(0)
+    G = casos.Gen(77, 32)
+    A, B = para_gpu(G.bloco(256, 1024, espalha=8)), para_gpu(G.bloco(128, 1024, espalha=8))
+    RA, RB = oc.max_linha(A), oc.max_linha(B)
+    assert torch.equal(RA.cpu(), A[1].cpu().amax(1)) and torch.equal(RB.cpu(), B[1].cpu().amax(1))
+    inteiro = oc.gemm(A, B, cru=True)
+    soma = None
+    for h in range(2):
+        a = (A[0][:, h * 512:(h + 1) * 512].contiguous(), A[1][:, h * 16:(h + 1) * 16].contiguous())
+        b = (B[0][:, h * 512:(h + 1) * 512].contiguous(), B[1][:, h * 16:(h + 1) * 16].contiguous())
+        acc, e = oc.gemm(a, b, cru=True, RA=RA, RB=RB)
+        assert torch.equal(e, inteiro[1])
+        soma = acc if soma is None else soma + acc
+    assert torch.equal(soma, inteiro[0])
+
+
+def test_sentinela_token_invalido(amb):
+    """An out-of-range token is recorded (code 6) and reported with operation and position; nothing traps."""
+    from jatai_b200.registro import ErroJatai
+    ops, oc, reg = amb
+    ops.define_blk(32)
+    reg.novo_passo(0)
+    G = casos.Gen(5, 32)
+    W = para_gpu(G.bloco(256, 128))
+    tok = G.tok(64, 256)
+    tok[17] = 300
+    reg.vigiar = False
+    try:
+        X = oc.embed(W, tok.to(DEV))
+        with pytest.raises(ErroJatai) as ei:
+            reg.confere_device()
+        assert "embed" in str(ei.value) and "linha 17" in str(ei.value) and "300" in str(ei.value)
+        assert int(X[0][17].abs().sum()) == 0 and int(X[1][17, 0]) == -127
+    finally:
+        reg.vigiar = True
+        reg.novo_passo(0)
+
+
+def test_referencia_compat(amb):
+    """Compatibility format (block 128): the reference's own CUDA library, compiled for sm_100a from its source,
+    is driven through the same operator class and must agree with this library bit for bit."""
+    caminho = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "oracle", "_ref", "libjatai_ref.so")
+    if not os.path.exists(caminho):
+        pytest.skip("oracle/_ref/libjatai_ref.so not built (needs the reference checkout at build time)")
+    from jatai_b200 import registro
+    ops, oc, reg = amb
+    ops.define_blk(128)
+    reg.novo_passo(0)
+    reg2 = registro.Registro(tempfile.mkdtemp(), "ref", vigiar=True, eco=False, salvar=False)
+    ocr = ops.OpsCuda(reg2, biblioteca=caminho)
+    ops.OpsCuda.lib_global = oc.lib
+    reg2.novo_passo(0)
+    G = casos.Gen(9, 128)
+    M, D, FF = 256, 256, 1024
+    x, w1, w2, r = para_gpu(G.bloco(M, D)), para_gpu(G.bloco(FF, D)), para_gpu(G.bloco(D, FF)), para_gpu(G.bloco(M, D, espalha=8))
+    for nome, f in [("gemm", lambda o: o.gemm(x, w1)), ("gemm_cru", lambda o: o.gemm(x, w1, cru=True)),
+                    ("gemm_relu2", lambda o: o.gemm_relu2(x, w1)), ("gemm_soma", lambda o: o.gemm_soma(o.gemm_relu2(x, w1)[1], w2, r)),
+                    ("transpoe", lambda o: o.transpoe(w1)), ("rms", lambda o: o.rms(x)), ("soma", lambda o: o.soma(x, r))]:
+        a, b = casos.plano(f(oc)), casos.plano(f(ocr))
+        torch.cuda.synchronize()
+        compara(f"ref/{nome}", a, b)
