@@ -210,3 +210,34 @@ def test_referencia_compat(amb):
         a, b = casos.plano(f(oc)), casos.plano(f(ocr))
         torch.cuda.synchronize()
         compara(f"ref/{nome}", a, b)
+
+
+ATENCOES = [  # blk, Bt, T, H, D  (head dim D/H in {4, 16, 64}; T also off the 128 grid; block 128 with wide heads)
+    (32, 2, 64, 4, 64), (32, 2, 128, 2, 128), (32, 1, 256, 8, 512), (32, 1, 160, 2, 128), (32, 2, 96, 16, 64),
+    (128, 2, 64, 2, 128), (128, 1, 192, 8, 128), (32, 1, 512, 2, 128),
+]
+
+
+@pytest.mark.parametrize("limite", [False, True])
+@pytest.mark.parametrize("blk,Bt,T,H,D", ATENCOES)
+def test_atencao_generalizada(amb, blk, Bt, T, H, D, limite):
+    """Attention forward + backward at head dimensions and sequence lengths the reference kernels do not reach,
+    against the generalised oracle (which reduces to the reference at head dimension 4)."""
+    ops, oc, reg = amb
+    ops.define_blk(blk)
+    reg.novo_passo(0)
+    G = casos.Gen(31 * T + H + D + blk, blk)
+    M = Bt * T
+    qkv, go = G.bloco(M, 3 * D, espalha=5, zera=0.05), G.bloco(M, D, e0=-20, espalha=6, zera=0.05)
+    s = spec.Spec(blk, limite=limite)
+    (o_r, P_r) = s.atencao(qkv, Bt, T, H)
+    g_r = s.atencao_back(go, qkv, P_r, Bt, T, H)
+    ops.ATENCAO_LIMITE = limite
+    try:
+        o_c, P_c = oc.atencao(para_gpu(qkv), Bt, T, H)
+        g_c = oc.atencao_back(para_gpu(go), para_gpu(qkv), P_c, Bt, T, H)
+        torch.cuda.synchronize()
+    finally:
+        ops.ATENCAO_LIMITE = False
+    compara(f"atencao {blk}/{Bt}/{T}/{H}/{D}", [*o_c, P_c], [*o_r, P_r])
+    compara(f"atencao_back {blk}/{Bt}/{T}/{H}/{D} limite={limite}", list(g_c), list(g_r))
