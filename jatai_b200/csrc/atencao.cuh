@@ -463,10 +463,22 @@ static size_t g_at_ws_ints = 0;
 
 static int at_log2(int x) { int k = 0; while ((1 << k) < x) k++; return (1 << k) == x ? k : -1; }
 
-template <typename K>
-static cudaError_t at_smem(K kern, size_t bytes) {
-    return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+// raises a kernel's dynamic shared-memory limit; remembered per kernel, so a repeated launch makes no runtime call
+static cudaError_t at_smem_ptr(const void* kern, size_t bytes) {
+    static const void* quem[64];
+    static size_t quanto[64];
+    static int n = 0;
+    int i = 0;
+    while (i < n && quem[i] != kern) i++;
+    if (i < n && bytes <= quanto[i]) return cudaSuccess;
+    cudaError_t c = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (c != cudaSuccess) return c;
+    if (i == n && n < 64) { quem[n] = kern; n++; }
+    if (i < 64) quanto[i] = bytes;
+    return cudaSuccess;
 }
+template <typename K>
+static cudaError_t at_smem(K kern, size_t bytes) { return at_smem_ptr(reinterpret_cast<const void*>(kern), bytes); }
 
 static bool at_valido(int blk, int Bt, int T, int H, int D, int* hd, int* lg2) {
     if (Bt <= 0 || T <= 0 || H <= 0 || D <= 0 || D % H) return false;

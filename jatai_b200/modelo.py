@@ -1,0 +1,180 @@
+"""The integer-only Transformer training step, written purely against the operator API.
+
+Host-side mirror of the reference's jatai_cuda/modelo.py (Modelo :29-140, PassoGravado :143-180): pre-norm
+Transformer, RMSNorm without gain, causal ALiBi attention, ReLU^2 MLP, byte vocabulary, q/k/v in one [3D, D]
+matrix; SGD with momentum 7/8, learning rate 2^-k, error feedback on the weights.  The same code runs on the
+CUDA launcher (`ops.OpsCuda`) and on any object with the same methods (the tests drive it with the int64
+oracle on CPU), because it only ever calls `self.ops.<op>(...)` and the registry's `trecho()`.
+
+Same constructor, same `passo(tok, alvo, k_lr)`, same weight names and the same seeded initialisation (generator
+and draw order of modelo.py:16-19,32-40) as the reference, so a run here and a run of the reference model start
+from identical weights.  Not included: the reference's opt-in 16-bit residual stream (JATAI_RES16).
+
+Data parallel: pass `redutor` (see jatai_b200.paralelo).  Every op except the weight-gradient GEMMs is per token
+or per sequence; the weight-gradient GEMM reduces over tokens, so ranks first agree on the row-maximum exponents
+(MAX), run the GEMM on their own tokens with those, and add the int32 partial sums (SUM).  Integer addition is
+associative, so the result is bit-identical to one GPU running the concatenated batch.
+"""
+import math
+
+import torch
+
+from . import ops as O
+
+
+def inicial(g, linhas, fan_in, dev, emb=False):
+    """Seeded initial weight block tensor: mantissa round(32 N(0,1)), one exponent for the whole tensor."""
+    e = -5 if emb else -int(round(math.log2(32 * math.sqrt(fan_in))))
+    m = torch.round(torch.randn(linhas, fan_in, generator=g) * 32).clamp(-127, 127).to(torch.int8)
+    E = torch.full((linhas, fan_in // O.BLK), e, dtype=torch.int8, device=dev)
+    return m.to(dev).contiguous(), E
+
+
+def zeros_como(t):
+    return torch.zeros_like(t[0]), torch.full_like(t[1], O.E_ZERO)
+
+
+class Modelo:
+    def __init__(self, V, D, H, FF, L, semente, dev, ops, reg, redutor=None):
+        self.V, self.D, self.H, self.FF, self.L = V, D, H, FF, L
+        self.dev, self.ops, self.reg, self.redutor = dev, ops, reg, redutor
+        g = torch.Generator().manual_seed(semente)
+        p = {"emb": inicial(g, V, D, dev, emb=True)}
+        for l in range(L):
+            qkv = [inicial(g, D, D, dev) for _ in range(3)]
+            p[f"Wqkv{l}"] = (torch.cat([t[0] for t in qkv]).contiguous(), torch.cat([t[1] for t in qkv]).contiguous())
+            p[f"Wo{l}"] = inicial(g, D, D, dev)
+            p[f"Wup{l}"] = inicial(g, FF, D, dev)
+            p[f"Wd{l}"] = inicial(g, D, FF, dev)
+        p["out"] = inicial(g, V, D, dev)
+        self.p = p
+        self.mom = {n: zeros_como(t) for n, t in p.items()}
+        self.res = {n: zeros_como(t) for n, t in p.items()}
+        self.error_feedback = True
+        self.estatisticas = False
+
+    # ------------------------------------------------------------------ helpers
+    def _st(self, nome, t, zeros_normais=False):
+        if self.estatisticas:
+            self.reg.estatistica(nome, t, zeros_normais)
+
+    def _grad_peso(self, gy, x):
+        """dW = gy^T . x as a raw tensor.  Both operands are transposed so that the reduced dimension (tokens)
+        is the blocked one.  With a reducer the ranks align to common row maxima and add their partial sums."""
+        ops = self.ops
+        a, b = ops.transpoe(gy), ops.transpoe(x)
+        if self.redutor is None:
+            return ops.gemm(a, b, cru=True)
+        RA, RB = self.redutor.maximos(ops.max_linha(a), ops.max_linha(b))
+        acc, e = ops.gemm(a, b, cru=True, RA=RA, RB=RB)
+        return self.redutor.soma(acc), e
+
+    # ------------------------------------------------------------------ the step
+    def passo(self, tok, alvo, k_lr=None):
+        """Forward (+ backward and update when k_lr is given).  Returns the loss as a tensor (report only, float)."""
+        ops, reg, p = self.ops, self.reg, self.p
+        Bt, T = tok.shape
+        tok = tok.reshape(-1).to(torch.int32).contiguous()
+        alvo = alvo.reshape(-1).to(torch.int32).contiguous()
+        guardados = []
+        with reg.trecho("forward"):
+            with reg.trecho("embedding"):
+                x = ops.embed(p["emb"], tok)
+            for l in range(self.L):
+                with reg.trecho(f"camada {l}"):
+                    with reg.trecho("atencao"):
+                        n1, c1 = ops.rms(x)
+                        qkv = ops.gemm(n1, p[f"Wqkv{l}"])
+                        oc, P = ops.atencao(qkv, Bt, T, self.H)
+                        om = ops.quant(oc)
+                        x = ops.gemm_soma(om, p[f"Wo{l}"], x)
+                        self._st(f"c{l}.qkv", qkv); self._st(f"c{l}.atencao_saida", om); self._st(f"c{l}.residuo1", x)
+                    with reg.trecho("mlp"):
+                        n2, c2 = ops.rms(x)
+                        h, a = ops.gemm_relu2(n2, p[f"Wup{l}"])
+                        x = ops.gemm_soma(a, p[f"Wd{l}"], x)
+                        self._st(f"c{l}.relu2", a, zeros_normais=True); self._st(f"c{l}.residuo2", x)
+                guardados.append((n1, c1, qkv, P, om, n2, c2, h, a))
+            with reg.trecho("saida"):
+                nf, cf = ops.rms(x)
+                logits = ops.gemm(nf, p["out"], cru=True)
+                if self.redutor is None:
+                    g, d_alvo, soma = ops.softmax_ce(logits, alvo)
+                else:
+                    g, d_alvo, soma = ops.softmax_ce(logits, alvo, log2M=self.redutor.log2_tokens(tok.numel()))
+        # loss report: stays on the device; the caller converts after the step without stalling the queue
+        perda = (d_alvo.double() / 256 + torch.log(soma.double() / 4096)).mean()
+        if k_lr is None:
+            return perda
+        T_ = ops.transpoe
+        grads = {}
+        with reg.trecho("backward"):
+            with reg.trecho("saida"):
+                grads["out"] = self._grad_peso(g, nf)
+                gx = ops.rms_back(ops.gemm(g, T_(p["out"])), nf, cf)
+                self._st("grad_saida", gx)
+            for l in reversed(range(self.L)):
+                n1, c1, qkv, P, om, n2, c2, h, a = guardados[l]
+                with reg.trecho(f"camada {l}"):
+                    with reg.trecho("mlp"):
+                        grads[f"Wd{l}"] = self._grad_peso(gx, a)
+                        gh = ops.gemm_relu2_back(gx, T_(p[f"Wd{l}"]), h)
+                        grads[f"Wup{l}"] = self._grad_peso(gh, n2)
+                        gn = ops.gemm(gh, T_(p[f"Wup{l}"]))
+                        gx = ops.soma(gx, ops.rms_back(gn, n2, c2))
+                        self._st(f"c{l}.grad_mlp", gh, zeros_normais=True)
+                    with reg.trecho("atencao"):
+                        grads[f"Wo{l}"] = self._grad_peso(gx, om)
+                        go = ops.gemm(gx, T_(p[f"Wo{l}"]))
+                        gq = ops.quant(ops.atencao_back(go, qkv, P, Bt, T, self.H))
+                        grads[f"Wqkv{l}"] = self._grad_peso(gq, n1)
+                        gn = ops.gemm(gq, T_(p[f"Wqkv{l}"]))
+                        gx = ops.soma(gx, ops.rms_back(gn, n1, c1))
+                        self._st(f"c{l}.grad_qkv", gq); self._st(f"c{l}.grad_residuo", gx)
+            with reg.trecho("embedding"):
+                grads["emb"] = self._grad_peso(ops.um_quente(tok, self.V), gx)
+        with reg.trecho("otimizador"):
+            for n, gr in grads.items():
+                with reg.trecho(n):
+                    self.mom[n] = ops.momento(gr, self.mom[n])
+                    self.p[n], self.res[n] = ops.peso(self.p[n], self.mom[n], self.res[n], k_lr, self.error_feedback)
+        return perda
+
+
+class PassoGravado:
+    """One training step recorded in a CUDA graph and replayed: the few hundred launches become one call.
+
+    Recording executes nothing (weights do not change while recording).  Everything the step allocates lives in
+    the graph's pool at fixed addresses; weights, momentum and residual are updated in place by the kernels, so
+    the graph stays valid.  Inputs go to fixed buffers (copy_) before each replay.  The launch list of the
+    recording is kept: the launch ids are baked into the kernel arguments, so a sentinel raised during a replay
+    names the same operation and section as it would in eager mode.  Run one eager step before recording (the
+    attention backward sizes its workspace on first use, which a capture does not allow).
+    """
+
+    def __init__(self, modelo, Bt, T, k_lr):
+        self.m, self.reg, self.k_lr = modelo, modelo.reg, k_lr
+        lib = modelo.ops.lib
+        self.tok = torch.zeros(Bt, T, dtype=torch.long, device=modelo.dev)
+        self.alvo = torch.zeros(Bt, T, dtype=torch.long, device=modelo.dev)
+        self.grafo = torch.cuda.CUDAGraph()
+        est, vig, perf = modelo.estatisticas, self.reg.vigiar, self.reg.perfil
+        modelo.estatisticas, self.reg.vigiar, self.reg.perfil = False, False, False     # nothing that synchronises while recording
+        torch.cuda.synchronize()
+        self.reg.lancamentos = []
+        try:
+            with torch.cuda.graph(self.grafo):
+                lib.jt_stream(torch.cuda.current_stream().cuda_stream)
+                self.perda = modelo.passo(self.tok, self.alvo, k_lr=k_lr)
+        finally:
+            lib.jt_stream(None)
+            modelo.estatisticas, self.reg.vigiar, self.reg.perfil = est, vig, perf
+        self.lancamentos = list(self.reg.lancamentos)
+        self.reg.info(f"step recorded in a CUDA graph: {len(self.lancamentos)} launches", lancamentos=len(self.lancamentos))
+
+    def __call__(self, tok, alvo):
+        self.tok.copy_(tok)
+        self.alvo.copy_(alvo)
+        self.reg.lancamentos = self.lancamentos
+        self.grafo.replay()
+        return self.perda

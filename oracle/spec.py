@@ -169,6 +169,10 @@ class Spec:
     def gemm_relu2_back(self, A, B, Hh):                            # ops.py:118-119
         return self.relu2_back(self.gemm(A, B), Hh)
 
+    def max_linha(self, X):
+        """Row-maximum exponents of a block tensor: the RA / RB of gemm_acc (ops.py:98)."""
+        return X[1].amax(1).to(torch.int8)
+
     def transpoe(self, X):                                          # ops.py:121-123
         m, E = X
         return quant(m.to(I64).t().contiguous(), expande(E, self.blk).t().contiguous(), self.blk)
