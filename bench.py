@@ -4,9 +4,10 @@
 
 Workloads (synthetic data with the shapes and value distributions BASELINE.json names: mantissas uniform in
 [-127,127], one exponent per 32-element K-block uniform in [-12,-4], seeded):
-  gemm   (default) block-32 INT8 GEMM trio of one linear layer at (M,K,N) = (16384,4096,4096):
+  passo  (default) one full training step of the 12-layer model (D=512, 8 heads, T=256, batch 8 = 2048 tokens per GPU),
+         replayed from a CUDA graph; metric = tokens/s.
+  gemm   block-32 INT8 GEMM trio of one linear layer at (M,K,N) = (16384,4096,4096):
          Y = X.W^T, dX = dY.T(W)^T, dW = T(dY).T(X)^T raw.  A step = the three GEMMs; metric = TOPS (2.M.N.K each).
-  passo  one full training step of the 12-layer model (D=512, 8 heads, T=256, batch 8); metric = tokens/s.
 With N > 1 (torchrun, one rank per GPU): gemm runs independent replicas (the path has no exchange step);
 passo is data parallel with the bit-exact gradient reduction of jatai_b200.paralelo.
 
@@ -259,6 +260,8 @@ def braco_gemm(args):
     ms_e2e = max_ranks(ini.elapsed_time(fim), mundo, dev) / e_steps
     tops_e2e = mundo * 3 * ops_por_gemm / (ms_e2e * 1e-3) / 1e12
 
+    if mundo > 1:
+        torch.distributed.destroy_process_group()
     if rank != 0:
         return
     pk = picos()
@@ -268,7 +271,7 @@ def braco_gemm(args):
         "metric": "int8_b32_gemm_tops", "value": tops, "unit": "TOPS", "n_gpus": mundo, "steps": args.steps, "warmup": max(args.warmup, 3),
         "ms_per_step": ms_passo, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8+int32",
         "data": "synthetic",
-        "config": {"workload": "gemm_b32_16384x4096x4096", "shape_MKN": [M, K, N], "block": BLK, "gemms_per_step": ["Y=X.W^T", "dX=dY.W", "dW=dY^T.X raw"],
+        "config": {"workload": f"gemm_b32_{M}x{K}x{N}", "shape_MKN": [M, K, N], "block": BLK, "gemms_per_step": ["Y=X.W^T", "dX=dY.W", "dW=dY^T.X raw"],
                    "l2": "inputs larger than L2 (288 MB of operands per step)", "parallelism": f"replicas x{mundo}",
                    "via": args.via if args.via is not None else 0},
         "ms_per_gemm": {"fwd": por_gemm[0], "dX": por_gemm[1], "dW_raw": por_gemm[2]},
@@ -288,27 +291,208 @@ def braco_gemm(args):
         except Exception as e:      # the baseline is a reported extra; the GPU numbers stand without it
             saida["cpu_baseline"] = {"value": None, "unit": "TOPS", "cores": 0, "kind": "port", "sample": f"failed: {e}"}
     print(json.dumps(saida))
+
+
+# ------------------------------------------------------------------------------------------------ training step
+PASSO = dict(V=256, D=512, H=8, FF=2048, L=12, Bt=8, T=256, k_lr=4)      # BASELINE config 4
+
+
+def lote_tokens(seed, Bt, T, V):
+    """Uniform random byte tokens; inputs and targets shifted by one (the reference's batch recipe, treino.py:41-44)."""
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randint(0, V, (Bt, T + 1), generator=g)
+    return x[:, :-1].contiguous(), x[:, 1:].contiguous()
+
+
+def cpu_passo_amostra(L_am=2, Bt_am=2):
+    """Times the int64 restatement of the specification on a reduced model (same D, heads, T, FF; fewer layers and
+    sequences), scaled to the full step by layer and sequence count.  Returns (tokens/s scaled, seconds, threads, text)."""
+    from jatai_b200 import modelo, ops, registro
+    from oracle import spec
+    c = PASSO
+    antes = ops.BLK
+    ops.BLK = BLK
+    try:
+        reg = registro.Registro(tempfile.mkdtemp(), "cpu", eco=False)
+        m = modelo.Modelo(c["V"], c["D"], c["H"], c["FF"], L_am, 0, "cpu", spec.Spec(BLK), reg)
+        tok, alvo = lote_tokens(1, Bt_am, c["T"], c["V"])
+        t0 = time.perf_counter()
+        m.passo(tok, alvo, k_lr=c["k_lr"])
+        dt = time.perf_counter() - t0
+    finally:
+        ops.BLK = antes
+    # per-layer work dominates; embedding/logits (1 of ~13 layer-equivalents) are counted with the layers
+    escala = (c["L"] / L_am)
+    tps = Bt_am * c["T"] / (dt * escala)
+    return tps, dt, torch.get_num_threads(), (f"{L_am} of {c['L']} layers, {Bt_am} of {c['Bt']} sequences of T={c['T']}, int64 torch restatement "
+                                              f"of the spec, {dt:.1f} s; tokens/s scaled by the layer count")
+
+
+def braco_referencia_passo(args):
+    rank, _, _ = dist_info()
+    if rank != 0:
+        return
+    vals = []
+    for i in range(min(args.warmup, 1) + min(args.steps, 3)):
+        tps, dt, th, txt = cpu_passo_amostra()
+        if i >= min(args.warmup, 1):
+            vals.append((tps, dt))
+    tps = sum(v for v, _ in vals) / len(vals)
+    c = PASSO
+    print(json.dumps({
+        "impl": "reference", "metric": "train_tokens_per_s", "value": tps, "unit": "tokens/s", "n_gpus": args.gpus, "steps": len(vals),
+        "warmup": min(args.warmup, 1), "ms_per_step": 1e3 * sum(d for _, d in vals) / len(vals), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "int8+int32", "data": "synthetic",
+        "config": {"workload": f"passo_{c['L']}L_D{c['D']}_H{c['H']}_T{c['T']}_Bt{c['Bt']}_b{BLK}", "sample": txt},
+        "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": th, "kind": "port", "sample": txt},
+        "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}))
+
+
+def resumo_perfil(reg, pk):
+    """Per-operation GPU time of one eager step (CUDA events around every launch) and the roofline of the GEMMs."""
+    tempos, ops_gemm, ms_gemm = {}, 0.0, 0.0
+    for (op, ini, fim), lanc in zip(reg.eventos, reg.lancamentos):
+        ms = ini.elapsed_time(fim)
+        tempos[op] = tempos.get(op, 0.0) + ms
+        if op.startswith("gemm"):
+            a, b = lanc["entradas"]["A"], lanc["entradas"]["B"]
+            ops_gemm += 2.0 * a.shape[0] * a.shape[1] * b.shape[0]
+            ms_gemm += ms
+    total = sum(tempos.values())
+    ordem = sorted(tempos.items(), key=lambda kv: -kv[1])
+    return {"ms_per_op": {k: round(v, 4) for k, v in ordem}, "ms_total": total, "gemm_ops": ops_gemm, "gemm_ms": ms_gemm}
+
+
+def braco_passo(args):
+    rank, local, mundo = dist_info()
+    if mundo > 1:
+        torch.cuda.set_device(local)
+        torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", local))
+    dev = torch.device("cuda", local if mundo > 1 else 0)
+    torch.cuda.set_device(dev)
+    from jatai_b200 import modelo, ops, paralelo, registro
+    ops.define_blk(BLK)
+    c = PASSO
+    reg = registro.Registro(tempfile.mkdtemp(), f"passo{rank}", eco=False, salvar=False)
+    oc = ops.OpsCuda(reg)
+    if args.via is not None:
+        assert oc.lib.jt_gemm_via(args.via) == 0
+    red = paralelo.Redutor() if mundo > 1 else None
+    m = modelo.Modelo(c["V"], c["D"], c["H"], c["FF"], c["L"], 0, dev, oc, reg, redutor=red)
+    Bt, T = c["Bt"], c["T"]
+    lotes = [tuple(t.to(dev) for t in lote_tokens(100 * rank + i, Bt, T, c["V"])) for i in range(8)]
+    # one eager step with per-launch events: sizes the attention workspace, gives the per-op breakdown
+    reg.perfil = True
+    reg.novo_passo(0)
+    m.passo(*lotes[0], k_lr=c["k_lr"])
+    reg.fim_passo()
+    perfil = resumo_perfil(reg, picos())
+    lancamentos = len(reg.lancamentos)
+    reg.perfil = False
+    reg.tempos = {}
+    passo_fn = None
+    modo = "eager"
+    if not args.eager:
+        try:
+            gravado = modelo.PassoGravado(m, Bt, T, c["k_lr"])
+            passo_fn, modo = gravado, "cuda_graph"
+        except Exception as e:          # capture refused (e.g. a collective that can not be captured): run eagerly, say so
+            modo = f"eager (graph capture failed: {type(e).__name__})"
+    if passo_fn is None:
+        def passo_fn(tok, alvo):
+            reg.lancamentos = []
+            return m.passo(tok, alvo, k_lr=c["k_lr"])
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+    W = max(args.warmup, 3)
+    for i in range(W):
+        passo_fn(*lotes[i % 8])
+    barreira(mundo)
+    rel = Relogios(dev.index or 0)
+    ini, fim = ev(), ev()
+    ini.record()
+    for i in range(args.steps):
+        perda = passo_fn(*lotes[i % 8])
+    fim.record()
+    barreira(mundo)
+    ms = max_ranks(ini.elapsed_time(fim), mundo, dev) / args.steps
+    clocks = rel.fim()
+    n_err = reg.lib.jt_erro_le((ctypes.c_longlong * 6)())
+    assert n_err == 0, f"device error record has {n_err} events"
+    tps = mundo * Bt * T / (ms * 1e-3)
+    # end to end: tokens come from pinned host memory every step and the loss is read back every step
+    hospedeiro = [tuple(t.pin_memory() for t in lote_tokens(100 * rank + i, Bt, T, c["V"])) for i in range(8)]
+    perdas = []
+
+    def passo_e2e(i):
+        tok, alvo = hospedeiro[i % 8]
+        p = passo_fn(tok.to(dev, non_blocking=True), alvo.to(dev, non_blocking=True))
+        perdas.append(float(p))                      # device -> host read of the step's result (synchronises)
+
+    for i in range(2):
+        passo_e2e(i)
+    barreira(mundo)
+    ini.record()
+    for i in range(args.steps):
+        passo_e2e(i)
+    fim.record()
+    barreira(mundo)
+    ms_e2e = max_ranks(ini.elapsed_time(fim), mundo, dev) / args.steps
+    perda_f = float(perda)
     if mundo > 1:
         torch.distributed.destroy_process_group()
+    if rank != 0:
+        return
+    pk = picos()
+    pico_i8 = 2.0 * pk["bf16_sust"] if pk.get("bf16_sust") else 2.0 * pk["bf16"]
+    ach = perfil["gemm_ops"] / (perfil["gemm_ms"] * 1e-3) / 1e12 if perfil["gemm_ms"] else None
+    saida = {
+        "metric": "train_tokens_per_s", "value": tps, "unit": "tokens/s", "n_gpus": mundo, "steps": args.steps, "warmup": W,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8+int32", "data": "synthetic",
+        "config": {"workload": f"passo_{c['L']}L_D{c['D']}_H{c['H']}_T{c['T']}_Bt{c['Bt']}_b{BLK}", "tokens_per_gpu_step": Bt * T,
+                   "global_tokens_per_step": mundo * Bt * T, "block": BLK, "mode": modo, "parallelism": f"dp{mundo}",
+                   "l2": "weights + momentum + residual + activations of a step exceed L2 (about 0.6 GB touched per step)",
+                   "init": "seeded random weights (reference recipe), uniform random byte tokens"},
+        "loss_last": perda_f, "launches_per_step": lancamentos,
+        "roofline": {"bound": "tensor", "achieved": ach, "peak": pico_i8, "unit": "TOPS", "frac": (ach / pico_i8) if ach else None, "traffic": None,
+                     "kernel": "all block GEMMs of one step (k_gemm_tc / k_gemm_simt), CUDA events around every launch of one eager step",
+                     "peak_source": f"2 x cuBLAS bf16 sustained ({pk['origem']})", "gemm_ms_per_step": perfil["gemm_ms"]},
+        "ms_per_op_eager": perfil["ms_per_op"], "clocks": clocks,
+        "e2e": {"value": mundo * Bt * T / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": 2 * Bt * T * 8, "d2h_bytes_per_step": 8,
+                "ms_per_step": ms_e2e, "includes": "tokens and targets from pinned host memory, the step, loss read back to the host every step"},
+        "gpu_launches": lancamentos * args.steps,
+    }
+    if red is not None:
+        saida["wire"] = {"collectives_per_step": red.chamadas // (W + 2 * args.steps + 3) if modo == "eager" else None,
+                         "sum_bytes_per_step": sum(t[0].numel() for t in m.p.values()) * 4}
+    if mundo == 1 and not args.sem_cpu:
+        try:
+            ctps, dt, th, txt = cpu_passo_amostra()
+            saida["cpu_baseline"] = {"value": ctps, "unit": "tokens/s", "cores": th, "kind": "port", "sample": txt}
+        except Exception as e:
+            saida["cpu_baseline"] = {"value": None, "unit": "tokens/s", "cores": 0, "kind": "port", "sample": f"failed: {e}"}
+    print(json.dumps(saida))
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="gemm", choices=["gemm", "passo"])
+    ap.add_argument("--workload", default="passo", choices=["gemm", "passo"])
     ap.add_argument("--via", type=int, default=None, help="force a GEMM path (jt_gemm_via)")
+    ap.add_argument("--eager", action="store_true", help="passo: no CUDA graph")
+    ap.add_argument("--forma", type=int, nargs=3, default=None, metavar=("M", "K", "N"), help="gemm: another shape (profiling captures)")
     ap.add_argument("--sem-cpu", dest="sem_cpu", action="store_true", help="skip the cpu_baseline leg")
     args = ap.parse_args()
+    if args.forma:
+        FORMA.update(M=args.forma[0], K=args.forma[1], N=args.forma[2])
     if args.impl == "reference":
-        return braco_referencia(args)
+        return braco_referencia_passo(args) if args.workload == "passo" else braco_referencia(args)
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (there is no CPU path)")
     if args.workload == "passo":
-        from jatai_b200 import bench_passo
-        return bench_passo.roda(args)
+        return braco_passo(args)
     return braco_gemm(args)
 
 

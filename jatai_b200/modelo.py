@@ -12,8 +12,9 @@ from identical weights.  Not included: the reference's opt-in 16-bit residual st
 
 Data parallel: pass `redutor` (see jatai_b200.paralelo).  Every op except the weight-gradient GEMMs is per token
 or per sequence; the weight-gradient GEMM reduces over tokens, so ranks first agree on the row-maximum exponents
-(MAX), run the GEMM on their own tokens with those, and add the int32 partial sums (SUM).  Integer addition is
-associative, so the result is bit-identical to one GPU running the concatenated batch.
+(MAX), run the GEMM on their own tokens with those, and after the backward add all int32 partial sums in one
+collective (SUM).  Integer addition is associative, so the result is bit-identical to one GPU running the
+concatenated batch.
 """
 import math
 
@@ -66,8 +67,7 @@ class Modelo:
         if self.redutor is None:
             return ops.gemm(a, b, cru=True)
         RA, RB = self.redutor.maximos(ops.max_linha(a), ops.max_linha(b))
-        acc, e = ops.gemm(a, b, cru=True, RA=RA, RB=RB)
-        return self.redutor.soma(acc), e
+        return ops.gemm(a, b, cru=True, RA=RA, RB=RB)          # partial sums; added over ranks after the backward
 
     # ------------------------------------------------------------------ the step
     def passo(self, tok, alvo, k_lr=None):
@@ -133,6 +133,9 @@ class Modelo:
                         self._st(f"c{l}.grad_qkv", gq); self._st(f"c{l}.grad_residuo", gx)
             with reg.trecho("embedding"):
                 grads["emb"] = self._grad_peso(ops.um_quente(tok, self.V), gx)
+        if self.redutor is not None:
+            with reg.trecho("reducao"):
+                grads = self.redutor.soma_tudo(grads)
         with reg.trecho("otimizador"):
             for n, gr in grads.items():
                 with reg.trecho(n):

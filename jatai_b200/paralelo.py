@@ -8,7 +8,8 @@ parallelism is exactly a partition of it.  So, per weight tensor:
   1. each rank computes the row maxima of its own operands (jt_max_linha),
   2. all-reduce MAX of those int8 vectors (a few KB),
   3. each rank runs the GEMM on its tokens with the global maxima -> int32 partial sums with one common exponent,
-  4. all-reduce SUM of the int32 sums: exact, and the same bits whatever order the library adds in,
+  4. after the backward, ONE all-reduce SUM of all int32 sums of the step (a flat buffer): exact, and the same
+     bits whatever order the library adds in,
   5. every rank applies the same momentum / weight update, so weights stay identical without a broadcast.
 Requirements: equal token counts per rank, a multiple of 128 (the transposition tile); the global token count a
 power of two (softmax_ce averages by a shift).  The result equals one GPU running the concatenated batch.
@@ -44,12 +45,24 @@ class Redutor:
         self.chamadas += 1
         return junto[:RA.numel()].contiguous(), junto[RA.numel():].contiguous()
 
-    def soma(self, acc):
-        """Exact integer sum of the ranks' int32 partial accumulators (in place)."""
-        dist.all_reduce(acc, op=dist.ReduceOp.SUM, group=self.grupo)
-        self.bytes_soma += acc.numel() * 4
+    def soma_tudo(self, grads):
+        """Exact integer sum over ranks of every weight gradient of a step, as ONE collective: the int32 partial
+        accumulators are packed into a flat buffer (kept between steps), all-reduced with SUM and handed back as
+        views.  The exponents are equal on all ranks by construction and are not exchanged."""
+        total = sum(acc.numel() for acc, _ in grads.values())
+        algum = next(iter(grads.values()))[0]
+        if getattr(self, "_plano", None) is None or self._plano.numel() != total or self._plano.device != algum.device:
+            self._plano = torch.empty(total, dtype=torch.int32, device=algum.device)
+        o, vistas = 0, {}
+        for n, (acc, e) in grads.items():
+            v = self._plano[o:o + acc.numel()].view(acc.shape)
+            v.copy_(acc)
+            vistas[n] = (v, e)
+            o += acc.numel()
+        dist.all_reduce(self._plano, op=dist.ReduceOp.SUM, group=self.grupo)
+        self.bytes_soma += total * 4
         self.chamadas += 1
-        return acc
+        return vistas
 
 
 def media_da_perda(perda, grupo=None):
