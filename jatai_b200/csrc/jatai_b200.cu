@@ -294,6 +294,44 @@ int jt_atencao_back(const void* gom, const void* goE, const void* qm, const void
                         (int16_t*)Ge, Bt, T, H, D, GA, limite, kid, g_stream);
 }
 
+// Attention backward for callers that must not allocate device memory: a process that runs under a fixed memory
+// budget carved up before start-up, a host thread inside a stream capture or a callback where cudaMalloc is not
+// permitted, or an embedding runtime that forbids the library to touch the allocator at all.  jt_atencao_back
+// sizes its workspace with cudaMalloc on first use; this variant keeps the workspace (statistics + one s_lin per
+// query row = Bt*H*(8+T) ints) in the fixed array below instead, and calls no allocating routine.
+//   * limit: Bt*H*(8+T) <= JT_FIXO_INTS (2^20 ints = 4 MiB, resident on every GPU that loads the library until
+//     the process exits); larger problems are refused with cudaErrorInvalidValue and a message on stderr;
+//   * the first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device
+//     current) and remembers it; make that first call outside any stream capture;
+//   * every call shares the one array: the statistics slots are cleared at the start of each call, the s_lin
+//     slots are overwritten before they are read; two calls that overlap on the GPU (different streams) race.
+constexpr size_t JT_FIXO_INTS = (size_t)1 << 20;
+static __device__ __align__(256) int g_at_fixo[JT_FIXO_INTS];
+static int* g_at_fixo_end[64];          // device address of g_at_fixo, per device ordinal (host-side cache)
+
+int jt_atencao_back_fixo(const void* gom, const void* goE, const void* qm, const void* qE, const void* P, void* Gacc, void* Ge, int Bt,
+                         int T, int H, int D, int GA, int limite, int kid) {
+    if (Bt <= 0 || T <= 0 || H <= 0) return (int)cudaErrorInvalidValue;
+    const size_t precisa = (size_t)Bt * H * (at::N_EST + T);
+    if (precisa > JT_FIXO_INTS) {
+        fprintf(stderr, "jt_atencao_back_fixo: Bt*H*(8+T) = %zu ints exceeds the fixed workspace of %zu ints; use jt_atencao_back\n",
+                precisa, JT_FIXO_INTS);
+        return (int)cudaErrorInvalidValue;
+    }
+    int dev = 0;
+    cudaError_t c = cudaGetDevice(&dev);
+    if (c != cudaSuccess) return (int)c;
+    if (dev < 0 || dev >= 64) return (int)cudaErrorInvalidDevice;
+    if (!g_at_fixo_end[dev]) {
+        void* p = nullptr;
+        c = cudaGetSymbolAddress(&p, g_at_fixo);      // the symbol name is a host-side handle, not a device pointer
+        if (c != cudaSuccess) return (int)c;
+        g_at_fixo_end[dev] = static_cast<int*>(p);
+    }
+    return atencao_tras_ws(g_blk, (const int8_t*)gom, (const int8_t*)goE, (const int8_t*)qm, (const int8_t*)qE, (const uint8_t*)P, (int*)Gacc,
+                           (int16_t*)Ge, Bt, T, H, D, GA, limite, kid, g_stream, g_at_fixo_end[dev]);
+}
+
 // The 16-bit residual stream of the reference (jt_para16 / jt_para8 / jt_soma16) is an opt-in ablation without an
 // int64 specification; it is not part of this library.  The symbols exist so that the reference launcher's
 // restype loop (ops.py:301-304) finds them; calling one reports "not supported".
