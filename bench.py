@@ -462,8 +462,7 @@ def braco_passo(args):
         "gpu_launches": lancamentos * args.steps,
     }
     if red is not None:
-        saida["wire"] = {"collectives_per_step": red.chamadas // (W + 2 * args.steps + 3) if modo == "eager" else None,
-                         "sum_bytes_per_step": sum(t[0].numel() for t in m.p.values()) * 4}
+        saida["wire"] = {"collectives_per_step": 2, "max_bytes_per_step": int(red._max.numel()), "sum_bytes_per_step": int(red._plano.numel()) * 4}
     if mundo == 1 and not args.sem_cpu:
         try:
             ctps, dt, th, txt = cpu_passo_amostra()

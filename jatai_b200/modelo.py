@@ -12,9 +12,10 @@ from identical weights.  Not included: the reference's opt-in 16-bit residual st
 
 Data parallel: pass `redutor` (see jatai_b200.paralelo).  Every op except the weight-gradient GEMMs is per token
 or per sequence; the weight-gradient GEMM reduces over tokens, so ranks first agree on the row-maximum exponents
-(MAX), run the GEMM on their own tokens with those, and after the backward add all int32 partial sums in one
-collective (SUM).  Integer addition is associative, so the result is bit-identical to one GPU running the
-concatenated batch.
+(MAX), run the GEMM on their own tokens with those, and add the int32 partial sums (SUM).  A weight gradient feeds
+nothing but the optimiser, so all weight-gradient GEMMs are deferred to the end of the backward: a data-parallel step
+is forward + backward with no communication, ONE MAX collective, the deferred GEMMs, ONE SUM collective, the
+optimiser.  Integer addition is associative, so the result is bit-identical to one GPU running the concatenated batch.
 """
 import math
 
@@ -59,23 +60,55 @@ class Modelo:
         if self.estatisticas:
             self.reg.estatistica(nome, t, zeros_normais)
 
-    def _grad_peso(self, gy, x):
+    def _grad_peso(self, nome, gy, x):
         """dW = gy^T . x as a raw tensor.  Both operands are transposed so that the reduced dimension (tokens)
-        is the blocked one.  With a reducer the ranks align to common row maxima and add their partial sums."""
+        is the blocked one.  Data parallel: the GEMM is deferred - only the transposed operands and their row
+        maxima are kept - because a weight gradient feeds nothing but the optimiser; all of them run after the
+        backward, between the two collectives of the step (see `_gemms_adiados`)."""
         ops = self.ops
         a, b = ops.transpoe(gy), ops.transpoe(x)
         if self.redutor is None:
-            return ops.gemm(a, b, cru=True)
-        RA, RB = self.redutor.maximos(ops.max_linha(a), ops.max_linha(b))
-        return ops.gemm(a, b, cru=True, RA=RA, RB=RB)          # partial sums; added over ranks after the backward
+            self._grads[nome] = ops.gemm(a, b, cru=True)
+        else:
+            self._adiados.append((nome, a, b, ops.max_linha(a), ops.max_linha(b)))
+
+    def _gemms_adiados(self, maximos):
+        """Data parallel, after the MAX collective: every weight-gradient GEMM with the global row maxima."""
+        for (nome, a, b, _, _), (RA, RB) in zip(self._adiados, maximos):
+            with self.reg.trecho(nome):
+                self._grads[nome] = self.ops.gemm(a, b, cru=True, RA=RA, RB=RB)
+        self._adiados = []
+
+    def _otimiza(self, grads, k_lr):
+        ops = self.ops
+        for n, gr in grads.items():
+            with self.reg.trecho(n):
+                self.mom[n] = ops.momento(gr, self.mom[n])
+                self.p[n], self.res[n] = ops.peso(self.p[n], self.mom[n], self.res[n], k_lr, self.error_feedback)
 
     # ------------------------------------------------------------------ the step
     def passo(self, tok, alvo, k_lr=None):
         """Forward (+ backward and update when k_lr is given).  Returns the loss as a tensor (report only, float)."""
+        perda = self.frente_tras(tok, alvo, treina=k_lr is not None)
+        if k_lr is None:
+            return perda
+        grads = self._grads
+        if self.redutor is not None:
+            with self.reg.trecho("gradientes de peso"):
+                self._gemms_adiados(self.redutor.maximos_tudo([(ra, rb) for _, _, _, ra, rb in self._adiados]))
+                grads = self.redutor.soma_tudo(self._grads)
+        with self.reg.trecho("otimizador"):
+            self._otimiza(grads, k_lr)
+        return perda
+
+    def frente_tras(self, tok, alvo, treina=True):
+        """Forward and (if `treina`) backward.  Weight gradients land in self._grads (single GPU) or, data parallel,
+        their operands in self._adiados.  No communication happens here."""
         ops, reg, p = self.ops, self.reg, self.p
         Bt, T = tok.shape
         tok = tok.reshape(-1).to(torch.int32).contiguous()
         alvo = alvo.reshape(-1).to(torch.int32).contiguous()
+        self._grads, self._adiados = {}, []
         guardados = []
         with reg.trecho("forward"):
             with reg.trecho("embedding"):
@@ -104,43 +137,34 @@ class Modelo:
                     g, d_alvo, soma = ops.softmax_ce(logits, alvo, log2M=self.redutor.log2_tokens(tok.numel()))
         # loss report: stays on the device; the caller converts after the step without stalling the queue
         perda = (d_alvo.double() / 256 + torch.log(soma.double() / 4096)).mean()
-        if k_lr is None:
+        if not treina:
             return perda
         T_ = ops.transpoe
-        grads = {}
         with reg.trecho("backward"):
             with reg.trecho("saida"):
-                grads["out"] = self._grad_peso(g, nf)
+                self._grad_peso("out", g, nf)
                 gx = ops.rms_back(ops.gemm(g, T_(p["out"])), nf, cf)
                 self._st("grad_saida", gx)
             for l in reversed(range(self.L)):
                 n1, c1, qkv, P, om, n2, c2, h, a = guardados[l]
                 with reg.trecho(f"camada {l}"):
                     with reg.trecho("mlp"):
-                        grads[f"Wd{l}"] = self._grad_peso(gx, a)
+                        self._grad_peso(f"Wd{l}", gx, a)
                         gh = ops.gemm_relu2_back(gx, T_(p[f"Wd{l}"]), h)
-                        grads[f"Wup{l}"] = self._grad_peso(gh, n2)
+                        self._grad_peso(f"Wup{l}", gh, n2)
                         gn = ops.gemm(gh, T_(p[f"Wup{l}"]))
                         gx = ops.soma(gx, ops.rms_back(gn, n2, c2))
                         self._st(f"c{l}.grad_mlp", gh, zeros_normais=True)
                     with reg.trecho("atencao"):
-                        grads[f"Wo{l}"] = self._grad_peso(gx, om)
+                        self._grad_peso(f"Wo{l}", gx, om)
                         go = ops.gemm(gx, T_(p[f"Wo{l}"]))
                         gq = ops.quant(ops.atencao_back(go, qkv, P, Bt, T, self.H))
-                        grads[f"Wqkv{l}"] = self._grad_peso(gq, n1)
+                        self._grad_peso(f"Wqkv{l}", gq, n1)
                         gn = ops.gemm(gq, T_(p[f"Wqkv{l}"]))
                         gx = ops.soma(gx, ops.rms_back(gn, n1, c1))
                         self._st(f"c{l}.grad_qkv", gq); self._st(f"c{l}.grad_residuo", gx)
             with reg.trecho("embedding"):
-                grads["emb"] = self._grad_peso(ops.um_quente(tok, self.V), gx)
-        if self.redutor is not None:
-            with reg.trecho("reducao"):
-                grads = self.redutor.soma_tudo(grads)
-        with reg.trecho("otimizador"):
-            for n, gr in grads.items():
-                with reg.trecho(n):
-                    self.mom[n] = ops.momento(gr, self.mom[n])
-                    self.p[n], self.res[n] = ops.peso(self.p[n], self.mom[n], self.res[n], k_lr, self.error_feedback)
+                self._grad_peso("emb", ops.um_quente(tok, self.V), gx)
         return perda
 
 
@@ -152,7 +176,9 @@ class PassoGravado:
     the graph stays valid.  Inputs go to fixed buffers (copy_) before each replay.  The launch list of the
     recording is kept: the launch ids are baked into the kernel arguments, so a sentinel raised during a replay
     names the same operation and section as it would in eager mode.  Run one eager step before recording (the
-    attention backward sizes its workspace on first use, which a capture does not allow).
+    attention backward sizes its workspace on first use, which a capture does not allow).  Data parallel: the
+    step is recorded as three graphs (forward+backward | deferred weight-gradient GEMMs | optimiser) and the two
+    collectives run eagerly between the replays, on the same stream.
     """
 
     def __init__(self, modelo, Bt, T, k_lr):
@@ -160,24 +186,54 @@ class PassoGravado:
         lib = modelo.ops.lib
         self.tok = torch.zeros(Bt, T, dtype=torch.long, device=modelo.dev)
         self.alvo = torch.zeros(Bt, T, dtype=torch.long, device=modelo.dev)
-        self.grafo = torch.cuda.CUDAGraph()
         est, vig, perf = modelo.estatisticas, self.reg.vigiar, self.reg.perfil
         modelo.estatisticas, self.reg.vigiar, self.reg.perfil = False, False, False     # nothing that synchronises while recording
         torch.cuda.synchronize()
         self.reg.lancamentos = []
+        red = modelo.redutor
         try:
-            with torch.cuda.graph(self.grafo):
-                lib.jt_stream(torch.cuda.current_stream().cuda_stream)
-                self.perda = modelo.passo(self.tok, self.alvo, k_lr=k_lr)
+            if red is None:
+                self.grafos = [torch.cuda.CUDAGraph()]
+                with torch.cuda.graph(self.grafos[0]):
+                    lib.jt_stream(torch.cuda.current_stream().cuda_stream)
+                    self.perda = modelo.passo(self.tok, self.alvo, k_lr=k_lr)
+            else:
+                # Data parallel: three graphs with the two collectives issued eagerly between them, so that no
+                # collective is ever part of a captured graph.  The reducer's flat buffers must already exist with
+                # their final sizes (one eager step has run), so the graphs see fixed addresses.
+                assert getattr(red, "_max", None) is not None and getattr(red, "_plano", None) is not None, \
+                    "run one eager data-parallel step before recording"
+                self.grafos = [torch.cuda.CUDAGraph() for _ in range(3)]
+                with torch.cuda.graph(self.grafos[0]):
+                    lib.jt_stream(torch.cuda.current_stream().cuda_stream)
+                    self.perda = modelo.frente_tras(self.tok, self.alvo)
+                    pares = [(ra, rb) for _, _, _, ra, rb in modelo._adiados]
+                    red.empacota_maximos(pares)
+                with torch.cuda.graph(self.grafos[1], pool=self.grafos[0].pool()):
+                    lib.jt_stream(torch.cuda.current_stream().cuda_stream)
+                    modelo._gemms_adiados(red.vistas_maximos(pares))
+                    vistas = red.empacota_somas(modelo._grads)
+                with torch.cuda.graph(self.grafos[2], pool=self.grafos[0].pool()):
+                    lib.jt_stream(torch.cuda.current_stream().cuda_stream)
+                    with self.reg.trecho("otimizador"):
+                        modelo._otimiza(vistas, k_lr)
         finally:
             lib.jt_stream(None)
             modelo.estatisticas, self.reg.vigiar, self.reg.perfil = est, vig, perf
         self.lancamentos = list(self.reg.lancamentos)
-        self.reg.info(f"step recorded in a CUDA graph: {len(self.lancamentos)} launches", lancamentos=len(self.lancamentos))
+        self.reg.info(f"step recorded in {len(self.grafos)} CUDA graph(s): {len(self.lancamentos)} launches", lancamentos=len(self.lancamentos))
 
     def __call__(self, tok, alvo):
         self.tok.copy_(tok)
         self.alvo.copy_(alvo)
         self.reg.lancamentos = self.lancamentos
-        self.grafo.replay()
+        if len(self.grafos) == 1:
+            self.grafos[0].replay()
+        else:
+            red = self.m.redutor
+            self.grafos[0].replay()
+            red.reduz_maximos()
+            self.grafos[1].replay()
+            red.reduz_somas()
+            self.grafos[2].replay()
         return self.perda

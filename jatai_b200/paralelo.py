@@ -5,9 +5,10 @@ multi-GPU code; the scheme follows from its own split-K argument (jatai_cuda/jat
 of the reduced dimension of a block GEMM gives bit-identical sums PROVIDED every part aligns its partial products
 to the same row-maximum exponents.  In the weight-gradient GEMM the reduced dimension is the token axis, and data
 parallelism is exactly a partition of it.  So, per weight tensor:
-  1. each rank computes the row maxima of its own operands (jt_max_linha),
-  2. all-reduce MAX of those int8 vectors (a few KB),
-  3. each rank runs the GEMM on its tokens with the global maxima -> int32 partial sums with one common exponent,
+  1. each rank computes the row maxima of its own operands (jt_max_linha) during the backward,
+  2. after the backward, ONE all-reduce MAX of all those int8 vectors of the step (tens of KB),
+  3. each rank runs the (deferred) GEMMs on its tokens with the global maxima -> int32 partial sums with one
+     common exponent,
   4. after the backward, ONE all-reduce SUM of all int32 sums of the step (a flat buffer): exact, and the same
      bits whatever order the library adds in,
   5. every rank applies the same momentum / weight update, so weights stay identical without a broadcast.
@@ -37,18 +38,48 @@ class Redutor:
         assert 1 << k == n, f"global token count {n} is not a power of two"
         return k
 
-    def maximos(self, RA, RB):
-        """Global row-maximum exponents of both GEMM operands, one collective for the pair."""
-        junto = torch.cat([RA, RB])
-        dist.all_reduce(junto, op=dist.ReduceOp.MAX, group=self.grupo)
-        self.bytes_max += junto.numel()
+    def maximos_tudo(self, pares):
+        """Global row-maximum exponents of all deferred weight-gradient GEMMs of a step, as ONE collective.
+        `pares` = [(RA_local, RB_local), ...] int8 vectors; returns the same structure with the maxima over ranks
+        (views of a flat buffer kept between steps, so a captured graph finds them at fixed addresses)."""
+        total = sum(ra.numel() + rb.numel() for ra, rb in pares)
+        dev = pares[0][0].device
+        if getattr(self, "_max", None) is None or self._max.numel() != total or self._max.device != dev:
+            self._max = torch.empty(total, dtype=torch.int8, device=dev)
+        self.empacota_maximos(pares)
+        self.reduz_maximos()
+        return self.vistas_maximos(pares)
+
+    def empacota_maximos(self, pares):
+        o = 0
+        for ra, rb in pares:
+            for r in (ra, rb):
+                self._max[o:o + r.numel()].copy_(r)
+                o += r.numel()
+
+    def vistas_maximos(self, pares):
+        o, out = 0, []
+        for ra, rb in pares:
+            a = self._max[o:o + ra.numel()]
+            b = self._max[o + ra.numel():o + ra.numel() + rb.numel()]
+            out.append((a, b))
+            o += ra.numel() + rb.numel()
+        return out
+
+    def reduz_maximos(self):
+        dist.all_reduce(self._max, op=dist.ReduceOp.MAX, group=self.grupo)
+        self.bytes_max += self._max.numel()
         self.chamadas += 1
-        return junto[:RA.numel()].contiguous(), junto[RA.numel():].contiguous()
 
     def soma_tudo(self, grads):
         """Exact integer sum over ranks of every weight gradient of a step, as ONE collective: the int32 partial
         accumulators are packed into a flat buffer (kept between steps), all-reduced with SUM and handed back as
         views.  The exponents are equal on all ranks by construction and are not exchanged."""
+        vistas = self.empacota_somas(grads)
+        self.reduz_somas()
+        return vistas
+
+    def empacota_somas(self, grads):
         total = sum(acc.numel() for acc, _ in grads.values())
         algum = next(iter(grads.values()))[0]
         if getattr(self, "_plano", None) is None or self._plano.numel() != total or self._plano.device != algum.device:
@@ -59,10 +90,12 @@ class Redutor:
             v.copy_(acc)
             vistas[n] = (v, e)
             o += acc.numel()
-        dist.all_reduce(self._plano, op=dist.ReduceOp.SUM, group=self.grupo)
-        self.bytes_soma += total * 4
-        self.chamadas += 1
         return vistas
+
+    def reduz_somas(self):
+        dist.all_reduce(self._plano, op=dist.ReduceOp.SUM, group=self.grupo)
+        self.bytes_soma += self._plano.numel() * 4
+        self.chamadas += 1
 
 
 def media_da_perda(perda, grupo=None):

@@ -1,5 +1,6 @@
 """Data parallel on real GPUs (needs >= 2): two NCCL ranks, each with half of the sequences, must end two steps with
-exactly the weights, momentum and residual of one GPU running the whole batch."""
+exactly the weights, momentum and residual of one GPU running the whole batch (one eager step, then two steps
+replayed from CUDA graphs with the collectives between the graphs)."""
 import os
 import sys
 import tempfile
@@ -29,10 +30,14 @@ def _roda(dev, redutor, fatia):
     reg = registro.Registro(tempfile.mkdtemp(), "dp", eco=False, salvar=False)
     oc = ops.OpsCuda(reg)
     m = modelo.Modelo(CFG["V"], CFG["D"], CFG["H"], CFG["FF"], CFG["L"], 0, dev, oc, reg, redutor=redutor)
-    tok, alvo = _lote(1)
-    for p in range(2):
+    lotes = [_lote(s) for s in (1, 2, 3)]
+    reg.novo_passo(0)
+    m.passo(lotes[0][0][fatia].to(dev), lotes[0][1][fatia].to(dev), k_lr=4)           # eager
+    reg.fim_passo()
+    gravado = modelo.PassoGravado(m, fatia.stop - fatia.start, T, 4)                   # then replayed graphs
+    for p, (tok, alvo) in enumerate(lotes[1:], 1):
         reg.novo_passo(p)
-        m.passo(tok[fatia].to(dev), alvo[fatia].to(dev), k_lr=4)
+        gravado(tok[fatia].to(dev), alvo[fatia].to(dev))
         reg.fim_passo()
     return _estado(m)
 
