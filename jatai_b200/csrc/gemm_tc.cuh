@@ -10,10 +10,12 @@
 // instruction starts a fresh accumulator (tensor-memory stage) that is drained, aligned and added in registers;
 // with BLK = 128 four instructions accumulate in tensor memory before one drain.
 //
-// CTA = one 128 x 128 tile of C (optionally one K range of it: split-K for raw outputs), 10 warps:
-//   warp 0      TMA producer: A and B tiles of 128 rows x 128 bytes of K, SWIZZLE_128B, NST-stage ring
-//   warp 1      allocates tensor memory, issues the MMAs (one thread), frees tensor memory
-//   warps 2..9  drain: thread = one row of the tile (tcgen05.ld 32x32b), 64 columns each, then the output stage
+// CTA = one 128 x 128 tile of C (optionally one K range of it: split-K for raw outputs), 18 warps:
+//   warp 0       TMA producer (one lane): A and B tiles of 128 rows x 128 bytes of K, SWIZZLE_128B, NST-stage ring;
+//                all 32 lanes also build, ahead of the drain, the table of column scales 2^-(RB_j - eb_jb) it reads
+//   warp 1       allocates tensor memory, issues the MMAs (one thread), frees tensor memory
+//   warps 2..17  drain: thread = one row of the tile (tcgen05.ld 32x32b), 32 columns each (4 warps per scheduler hide
+//                the tensor-memory load latency), then the output stage
 // Every wait on an mbarrier is bounded: on a timeout the CTA records E_TEMPO, raises an abort flag that turns all
 // later waits into no-ops, and leaves through the normal exit (tensor memory is freed).
 #pragma once
@@ -23,14 +25,14 @@
 namespace jt {
 namespace tc {
 
-constexpr int TM = 128, KC = 128, NST = 4, NTM = 4, N_EPI = 256, N_THR = 320;
+constexpr int TM = 128, KC = 128, NST = 4, NTM = 4, NTB = 4, N_DW = 16, N_EPI = N_DW * 32, N_THR = 64 + N_EPI;
 constexpr uint32_t A_BYTES = TM * KC, B_BYTES = TN * KC, STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr uint32_t OFF_ACC = NST * STAGE_BYTES;
-constexpr uint32_t OFF_TAB = OFF_ACC + TM * PITCH * 4;
-constexpr uint32_t OFF_RA = OFF_TAB + 2 * 4 * TN * 4;
+constexpr uint32_t OFF_TAB = OFF_ACC + TM * PITCH * 4;                  // scale table ring: [NTB][4][TN] floats
+constexpr uint32_t OFF_RA = OFF_TAB + NTB * 4 * TN * 4;
 constexpr uint32_t OFF_RB = OFF_RA + TM * 4;
 constexpr uint32_t OFF_BAR = OFF_RB + TN * 4;
-constexpr uint32_t OFF_MISC = OFF_BAR + (2 * NST + 2 * NTM) * 8;
+constexpr uint32_t OFF_MISC = OFF_BAR + (2 * NST + 2 * NTM + 2 * NTB) * 8;
 constexpr uint32_t SMEM_BYTES = OFF_MISC + 16 + 1024;          // + slack to align the base to 1024 bytes
 constexpr long long LIMITE_CICLOS = 4000000000LL;              // ~2 s at B200 clocks
 constexpr uint32_t MAGIA = 0x4B400000u;                        // bit pattern of 1.5 * 2^23
@@ -94,16 +96,14 @@ constexpr uint32_t IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TN >
 #define JT_O4(a, i) "=r"(a[i]), "=r"(a[i + 1]), "=r"(a[i + 2]), "=r"(a[i + 3])
 #define JT_O16(a, i) JT_O4(a, i), JT_O4(a, i + 4), JT_O4(a, i + 8), JT_O4(a, i + 12)
 #define JT_O32(a, i) JT_O16(a, i), JT_O16(a, i + 16)
-// 64 consecutive columns of this thread's tensor-memory lane -> registers; returns when the data has arrived
-__device__ __forceinline__ void tmem_le64(uint32_t taddr, uint32_t (&d)[64]) {
+// 32 consecutive columns of this thread's tensor-memory lane -> registers; returns when the data has arrived
+__device__ __forceinline__ void tmem_le32(uint32_t taddr, uint32_t (&d)[32]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,"
-        "%24,%25,%26,%27,%28,%29,%30,%31}, [%64];\n"
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%32,%33,%34,%35,%36,%37,%38,%39,%40,%41,%42,%43,%44,%45,%46,%47,%48,%49,%50,%51,%52,%53,"
-        "%54,%55,%56,%57,%58,%59,%60,%61,%62,%63}, [%65];\n"
+        "%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
         "tcgen05.wait::ld.sync.aligned;\n"
-        : JT_O32(d, 0), JT_O32(d, 32)
-        : "r"(taddr), "r"(taddr + 32)
+        : JT_O32(d, 0)
+        : "r"(taddr)
         : "memory");
 }
 
@@ -121,10 +121,11 @@ __global__ void __launch_bounds__(N_THR, 1) k_gemm_tc(const __grid_constant__ CU
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_bruto + 1023) & ~(uintptr_t)1023);
     const uint32_t sbase = smem_u32(smem);
     int* acc_s = reinterpret_cast<int*>(smem + OFF_ACC);
-    float* tabB = reinterpret_cast<float*>(smem + OFF_TAB);          // [2][4][TN]
+    float* tabB = reinterpret_cast<float*>(smem + OFF_TAB);          // [NTB][4][TN]
     int* RAs = reinterpret_cast<int*>(smem + OFF_RA);
     int* RBs = reinterpret_cast<int*>(smem + OFF_RB);
     const uint32_t bar_full = sbase + OFF_BAR, bar_empty = bar_full + NST * 8, bar_tfull = bar_empty + NST * 8, bar_tempty = bar_tfull + NTM * 8;
+    const uint32_t bar_bfull = bar_tempty + NTM * 8, bar_bempty = bar_bfull + NTB * 8;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + OFF_MISC);
     volatile int* aborta = reinterpret_cast<volatile int*>(smem + OFF_MISC + 4);
 
@@ -136,7 +137,8 @@ __global__ void __launch_bounds__(N_THR, 1) k_gemm_tc(const __grid_constant__ CU
 
     if (tid == 0) {
         for (int i = 0; i < NST; i++) { mbar_init(bar_full + 8 * i, 1); mbar_init(bar_empty + 8 * i, 1); }
-        for (int i = 0; i < NTM; i++) { mbar_init(bar_tfull + 8 * i, 1); mbar_init(bar_tempty + 8 * i, N_EPI); }
+        for (int i = 0; i < NTM; i++) { mbar_init(bar_tfull + 8 * i, 1); mbar_init(bar_tempty + 8 * i, N_DW); }
+        for (int i = 0; i < NTB; i++) { mbar_init(bar_bfull + 8 * i, 32); mbar_init(bar_bempty + 8 * i, N_DW); }
         *aborta = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -150,15 +152,45 @@ __global__ void __launch_bounds__(N_THR, 1) k_gemm_tc(const __grid_constant__ CU
     const uint32_t tmem = *tmem_slot;
 
     if (wid == 0) {
-        // ------------------------------------------------------------------ TMA producer
-        if (lane == 0) {
-            for (int i = 0; i < pedacos_por_parte; i++) {
+        // ------------------------------------------------------------------ TMA producer + column scale tables
+        // lane l owns columns l, l+32, l+64, l+96 of the tile: their row maxima RB and, per chunk, their scales
+        int RBc[4];
+        const int8_t* ebc[4];
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            const int col = lane + 32 * k;
+            RBc[k] = RBg ? (int)RBg[n0 + col] : max_expoentes(EB + (size_t)(n0 + col) * nb, nb);
+            RBs[col] = RBc[k];
+            ebc[k] = EB + (size_t)(n0 + col) * nb + (size_t)ped0 * NQ;
+        }
+        bool ok = true;
+        for (int i = 0; i < pedacos_por_parte; i++) {
+            if (lane == 0 && ok) {
                 const int s = i % NST;
-                if (!espera(bar_empty + 8 * s, ((i / NST) & 1) ^ 1, aborta, kid, 1)) break;
-                mbar_expect_tx(bar_full + 8 * s, STAGE_BYTES);
-                tma_2d(sbase + s * STAGE_BYTES, &mapA, (ped0 + i) * KC, m0, bar_full + 8 * s);
-                tma_2d(sbase + s * STAGE_BYTES + A_BYTES, &mapB, (ped0 + i) * KC, n0, bar_full + 8 * s);
+                ok = espera(bar_empty + 8 * s, ((i / NST) & 1) ^ 1, aborta, kid, 1);
+                if (ok) {
+                    mbar_expect_tx(bar_full + 8 * s, STAGE_BYTES);
+                    tma_2d(sbase + s * STAGE_BYTES, &mapA, (ped0 + i) * KC, m0, bar_full + 8 * s);
+                    tma_2d(sbase + s * STAGE_BYTES + A_BYTES, &mapB, (ped0 + i) * KC, n0, bar_full + 8 * s);
+                }
             }
+            ok = __all_sync(FULL, ok);
+            if (!ok) break;
+            const int sl = i % NTB;
+            uint32_t w[4];
+#pragma unroll
+            for (int k = 0; k < 4; k++)
+                w[k] = NQ == 4 ? *reinterpret_cast<const uint32_t*>(ebc[k] + 4 * i) : (uint32_t)(uint8_t)ebc[k][i];
+            ok = __all_sync(FULL, espera(bar_bempty + 8 * sl, ((i / NTB) & 1) ^ 1, aborta, kid, 5));
+            if (!ok) break;
+#pragma unroll
+            for (int k = 0; k < 4; k++)
+#pragma unroll
+                for (int q = 0; q < NQ; q++) {
+                    const int sb = min(RBc[k] - (int)(int8_t)(w[k] >> (8 * q)), 40);
+                    tabB[(sl * 4 + q) * TN + lane + 32 * k] = pot2(-sb);
+                }
+            mbar_arrive(bar_bfull + 8 * sl);
         }
     } else if (wid == 1) {
         // ------------------------------------------------------------------ MMA issuer
@@ -193,60 +225,44 @@ __global__ void __launch_bounds__(N_THR, 1) k_gemm_tc(const __grid_constant__ CU
         }
     } else {
         // ------------------------------------------------------------------ drain + output stage
-        const int et = tid - 64;                                  // 0..255
+        const int et = tid - 64;                                  // 0..511
         const int quarto = wid & 3;                               // tensor-memory lanes this warp may read
-        const int metade = (wid - 2) >> 2;                        // column half of the tile
+        const int cg = (wid - 2) >> 2;                            // column group of 32 within the tile
         const int lin = quarto * 32 + lane;                       // row of the tile = tensor-memory lane
-        if (et < TM) RAs[et] = RAg ? (int)RAg[m0 + et] : max_expoentes(EA + (size_t)(m0 + et) * nb, nb);
-        else RBs[et - TM] = RBg ? (int)RBg[n0 + et - TM] : max_expoentes(EB + (size_t)(n0 + et - TM) * nb, nb);
-        asm volatile("bar.sync 1, %0;" ::"n"(N_EPI) : "memory");
-        const int RA = RAs[lin];
+        const int RA = RAg ? (int)RAg[m0 + lin] : max_expoentes(EA + (size_t)(m0 + lin) * nb, nb);
+        if (cg == 0) RAs[lin] = RA;
         const int8_t* ea_lin = EA + (size_t)(m0 + lin) * nb + (size_t)ped0 * NQ;
-        const int8_t* eb_col = EB + (size_t)(n0 + (et & (TN - 1))) * nb + (size_t)ped0 * NQ;
-        const int RBc = RBs[et & (TN - 1)];
-        // exponents of one chunk: NQ bytes per row
-        auto le_exp = [&](const int8_t* p, int c) -> uint32_t {
-            if (NQ == 4) return *reinterpret_cast<const uint32_t*>(p + 4 * c);
-            return (uint32_t)(uint8_t)p[c];
+        auto le_exp = [&](int c) -> uint32_t {
+            if (NQ == 4) return *reinterpret_cast<const uint32_t*>(ea_lin + 4 * c);
+            return (uint32_t)(uint8_t)ea_lin[c];
         };
-        auto grava_tab = [&](int buf, uint32_t w) {
+        uint32_t eaw = le_exp(0), eaw_prox = 0;
+        int acc[32];
 #pragma unroll
-            for (int q = 0; q < NQ; q++) {
-                const int sb = min(RBc - (int)(int8_t)(w >> (8 * q)), 40);
-                tabB[(buf * 4 + q) * TN + et] = pot2(-sb);
-            }
-        };
-        uint32_t eaw = le_exp(ea_lin, 0), eaw_prox = 0, ebw_prox = 0;
-        if (et < TN) grava_tab(0, le_exp(eb_col, 0));
-        int acc[64];
-#pragma unroll
-        for (int j = 0; j < 64; j++) acc[j] = 0;
+        for (int j = 0; j < 32; j++) acc[j] = 0;
         int f = 0;
         bool ok = true;
-        for (int c = 0; c < pedacos_por_parte; c++) {
-            // every drain thread passes this barrier once per chunk, aborted or not (no thread may be left waiting)
-            asm volatile("bar.sync 1, %0;" ::"n"(N_EPI) : "memory");
-            if (!ok) continue;
-            if (c + 1 < pedacos_por_parte) {
-                eaw_prox = le_exp(ea_lin, c + 1);
-                if (et < TN) ebw_prox = le_exp(eb_col, c + 1);
-            }
+        for (int c = 0; c < pedacos_por_parte && ok; c++) {
+            const int sl = c % NTB;
+            if (c + 1 < pedacos_por_parte) eaw_prox = le_exp(c + 1);
+            ok = __all_sync(FULL, espera(bar_bfull + 8 * sl, (c / NTB) & 1, aborta, kid, 6));
+            if (!ok) break;
 #pragma unroll 1
             for (int q = 0; q < NQ; q++, f++) {
                 const int t = f % NTM;
-                ok = espera(bar_tfull + 8 * t, (f / NTM) & 1, aborta, kid, 4);
-                ok = __all_sync(FULL, ok);
+                ok = __all_sync(FULL, espera(bar_tfull + 8 * t, (f / NTM) & 1, aborta, kid, 4));
                 if (!ok) break;
                 tc_fence_depois();
-                uint32_t d[64];
-                tmem_le64(tmem + ((uint32_t)(quarto * 32) << 16) + t * TN + metade * 64, d);
+                uint32_t d[32];
+                tmem_le32(tmem + ((uint32_t)(quarto * 32) << 16) + t * TN + cg * 32, d);
                 tc_fence_antes();
-                mbar_arrive(bar_tempty + 8 * t);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_tempty + 8 * t);
                 const int sa = min(RA - (int)(int8_t)(eaw >> (8 * q)), 40);
                 const float fa = pot2(GG - sa), cneg = -MAGIA_F * fa;
-                const float4* tb = reinterpret_cast<const float4*>(tabB + ((c & 1) * 4 + q) * TN + metade * 64);
+                const float4* tb = reinterpret_cast<const float4*>(tabB + (sl * 4 + q) * TN + cg * 32);
 #pragma unroll
-                for (int j4 = 0; j4 < 16; j4++) {
+                for (int j4 = 0; j4 < 8; j4++) {
                     const float4 fb = tb[j4];
                     const float fbv[4] = {fb.x, fb.y, fb.z, fb.w};
 #pragma unroll
@@ -258,17 +274,20 @@ __global__ void __launch_bounds__(N_THR, 1) k_gemm_tc(const __grid_constant__ CU
                     }
                 }
             }
-            if (ok && c + 1 < pedacos_por_parte && et < TN) grava_tab((c + 1) & 1, ebw_prox);
+            if (!ok) break;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_bempty + 8 * sl);
             eaw = eaw_prox;
         }
         if (VIA == 0) {
             const uint32_t vies = (uint32_t)nfatias * MAGIA;
 #pragma unroll
-            for (int j = 0; j < 64; j++) acc[j] = (int)((uint32_t)acc[j] - vies);
+            for (int j = 0; j < 32; j++) acc[j] = (int)((uint32_t)acc[j] - vies);
         }
 #pragma unroll
-        for (int j = 0; j < 64; j += 4)
-            *reinterpret_cast<int4*>(acc_s + lin * PITCH + metade * 64 + j) = make_int4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+        for (int j = 0; j < 32; j += 4)
+            *reinterpret_cast<int4*>(acc_s + lin * PITCH + cg * 32 + j) = make_int4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+        // the only barrier of the drain warps: reached by every drain thread exactly once, aborted or not
         asm volatile("bar.sync 1, %0;" ::"n"(N_EPI) : "memory");
         epilogo_tile<BLK, MODO, N_EPI>(acc_s, RAs, RBs, TM, m0, n0, N, S, gridDim.z > 1, blockIdx.z == 0, kid, et);
     }
