@@ -8,6 +8,7 @@ Workloads (synthetic data with the shapes and value distributions BASELINE.json 
          replayed from a CUDA graph; metric = tokens/s.
   gemm   block-32 INT8 GEMM trio of one linear layer at (M,K,N) = (16384,4096,4096):
          Y = X.W^T, dX = dY.T(W)^T, dW = T(dY).T(X)^T raw.  A step = the three GEMMs; metric = TOPS (2.M.N.K each).
+  ops    the bandwidth-bound fused ops at 16384 tokens x D=1024: achieved HBM GB/s per op (single GPU).
 With N > 1 (torchrun, one rank per GPU): gemm runs independent replicas (the path has no exchange step);
 passo is data parallel with the bit-exact gradient reduction of jatai_b200.paralelo.
 
@@ -472,13 +473,120 @@ def braco_passo(args):
     print(json.dumps(saida))
 
 
+# ------------------------------------------------------------------------------------------------ fused op suite
+def braco_ops(args):
+    """BASELINE config 3: the bandwidth-bound ops at 16384 tokens x D=1024 (block 32); achieved HBM GB/s per op from
+    the algorithmic bytes (inputs read once + outputs written once).  Inputs rotate over enough copies to exceed L2."""
+    rank, local, mundo = dist_info()
+    dev = torch.device("cuda", local if mundo > 1 else 0)
+    torch.cuda.set_device(dev)
+    from jatai_b200 import ops, registro
+    ops.define_blk(BLK)
+    reg = registro.Registro(tempfile.mkdtemp(), f"ops{rank}", eco=False, salvar=False)
+    oc = ops.OpsCuda(reg)
+    reg.novo_passo(0)
+    M, D, FF, V, NW = 16384, 1024, 4096, 256, 12 * 1024 * 1024
+    g = torch.Generator().manual_seed(7)
+
+    def bloco(R, C, e0=-10, esp=4):
+        m = torch.randint(-127, 128, (R, C), generator=g, dtype=torch.int32).to(torch.int8).to(dev)
+        E = (e0 + torch.randint(-esp, esp + 1, (R, C // BLK), generator=g)).to(torch.int8).to(dev)
+        return m, E
+
+    def cru(R, C, bits=24, e0=-30):
+        a = torch.randint(-(1 << bits), 1 << bits, (R, C), generator=g, dtype=torch.int32).to(dev)
+        e = (e0 + torch.randint(-3, 4, (R, C), generator=g)).to(torch.int16).to(dev)
+        return a, e
+
+    b1 = 1 + 1.0 / BLK                       # bytes per element of a block tensor
+    casos_ = []                               # (name, bytes, [callable per buffer copy])
+
+    def copias(f, n):
+        return [f() for _ in range(n)]
+
+    x = copias(lambda: bloco(M, D), 6)
+    casos_.append(("rms", M * (2 * D * b1 + 8), [lambda t=t: oc.rms(t) for t in x]))
+    ys = [oc.rms(t) for t in x]
+    gs = copias(lambda: bloco(M, D, e0=-20), 6)
+    casos_.append(("rms_back", M * (3 * D * b1 + 8), [lambda a=a, y=y: oc.rms_back(a, y[0], y[1]) for a, y in zip(gs, ys)]))
+    casos_.append(("soma", 3 * M * D * b1, [lambda a=a, b=b: oc.soma(a, b) for a, b in zip(x, gs)]))
+    h = copias(lambda: bloco(M, FF), 3)
+    h2 = copias(lambda: bloco(M, FF), 3)
+    casos_.append(("relu2", 2 * M * FF * b1, [lambda t=t: oc.relu2(t) for t in h]))
+    casos_.append(("relu2_back", 3 * M * FF * b1, [lambda a=a, b=b: oc.relu2_back(a, b) for a, b in zip(h, h2)]))
+    casos_.append(("transpoe", 2 * M * FF * b1, [lambda t=t: oc.transpoe(t) for t in h]))
+    c = copias(lambda: cru(M, D), 3)
+    casos_.append(("quant", M * D * (6 + b1), [lambda t=t: oc.quant(t) for t in c]))
+    lg = copias(lambda: cru(M, V, bits=22, e0=-20), 12)
+    alvo = torch.randint(0, V, (M,), generator=g).to(torch.int32).to(dev)
+    casos_.append(("softmax_ce", M * (V * 6 + 4 + V * b1 + 8), [lambda t=t: oc.softmax_ce(t, alvo) for t in lg]))
+    gw = copias(lambda: cru(3072, 4096, bits=26, e0=-45), 3)
+    mom = copias(lambda: bloco(3072, 4096, e0=-40), 3)
+    w = copias(lambda: bloco(3072, 4096, e0=-9), 3)
+    res = copias(lambda: bloco(3072, 4096, e0=-20), 3)
+    casos_.append(("momento", NW * (6 + 2 * b1), [lambda a=a, b=b: oc.momento(a, b) for a, b in zip(gw, mom)]))
+    casos_.append(("peso", NW * 5 * b1, [lambda a=a, b=b, r=r: oc.peso(a, b, r, 4, True) for a, b, r in zip(w, mom, res)]))
+    Bt, T, H = 16, 1024, 16
+    qkv = copias(lambda: bloco(M, 3 * D, esp=3), 2)
+    casos_.append(("atencao (16 seq x 16 heads x T=1024, hd 64)", M * 3 * D * b1 + M * D * 6 + Bt * H * T * T,
+                   [lambda t=t: oc.atencao(t, Bt, T, H) for t in qkv]))
+    pk = picos()
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+    tabela, tot_b, tot_ms = {}, 0.0, 0.0
+    reps = max(args.steps, 5)
+    corrente = torch.cuda.Stream()
+    for nome, nbytes, fs in casos_:
+        for i in range(max(args.warmup, 3)):
+            reg.lancamentos = []
+            fs[i % len(fs)]()
+        torch.cuda.synchronize()
+        # the calls are recorded in a CUDA graph and the replay is timed: kernels of 10-100 us would otherwise be
+        # timed at the rate the Python launcher can enqueue them
+        grafo = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(corrente):
+            with torch.cuda.graph(grafo, stream=corrente):
+                oc.lib.jt_stream(ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+                saidas = []
+                for i in range(reps):
+                    reg.lancamentos = []
+                    saidas.append(fs[i % len(fs)]())
+            oc.lib.jt_stream(None)
+            grafo.replay()
+            torch.cuda.synchronize()
+            a, b = ev(), ev()
+            a.record()
+            grafo.replay()
+            b.record()
+        torch.cuda.synchronize()
+        del saidas, grafo
+        ms = a.elapsed_time(b) / reps
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        tabela[nome] = {"ms": round(ms, 4), "MB": round(nbytes / 1e6, 1), "GB/s": round(gbs, 1), "frac_of_measured_hbm": round(gbs / pk["hbm_gbs"], 3)}
+        tot_b += nbytes
+        tot_ms += ms
+    n = reg.lib.jt_erro_le((ctypes.c_longlong * 6)())
+    assert n == 0, f"device error record has {n} events"
+    if rank != 0:
+        return
+    agg = tot_b / (tot_ms * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": "fused_ops_hbm_gbs", "value": agg, "unit": "GB/s", "n_gpus": 1, "steps": reps, "warmup": max(args.warmup, 3), "ms_per_step": tot_ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8+int32", "data": "synthetic",
+        "config": {"workload": "ops_16384tok_D1024_b32", "l2": "inputs rotate over copies totalling more than L2 (126 MB)",
+                   "timing": "each op recorded `steps` times in a CUDA graph over rotating inputs; the replay is timed with CUDA events"},
+        "per_op": tabela,
+        "roofline": {"bound": "hbm", "achieved": agg, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": agg / pk["hbm_gbs"], "traffic": None,
+                     "peak_source": f"STREAM-style copy ({pk['origem']})"},
+        "gpu_launches": reps * len(casos_)}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="passo", choices=["gemm", "passo"])
+    ap.add_argument("--workload", default="passo", choices=["gemm", "passo", "ops"])
     ap.add_argument("--via", type=int, default=None, help="force a GEMM path (jt_gemm_via)")
     ap.add_argument("--eager", action="store_true", help="passo: no CUDA graph")
     ap.add_argument("--forma", type=int, nargs=3, default=None, metavar=("M", "K", "N"), help="gemm: another shape (profiling captures)")
@@ -492,6 +600,8 @@ def main():
         raise SystemExit("bench.py needs a CUDA device (there is no CPU path)")
     if args.workload == "passo":
         return braco_passo(args)
+    if args.workload == "ops":
+        return braco_ops(args)
     return braco_gemm(args)
 
 
