@@ -54,6 +54,11 @@ class Modelo:
         self.res = {n: zeros_como(t) for n, t in p.items()}
         self.error_feedback = True
         self.estatisticas = False
+        # second stream for the weight-gradient GEMMs (single GPU, CUDA launcher only)
+        usa_lado = redutor is None and hasattr(ops, "lib") and torch.device(dev).type == "cuda"
+        self._lado = torch.cuda.Stream(device=dev) if usa_lado else None
+        na_gpu = redutor is not None and hasattr(ops, "lib") and torch.device(dev).type == "cuda"
+        self._ramos = [torch.cuda.Stream(device=dev) for _ in range(3)] if na_gpu else []
 
     # ------------------------------------------------------------------ helpers
     def _st(self, nome, t, zeros_normais=False):
@@ -66,17 +71,51 @@ class Modelo:
         maxima are kept - because a weight gradient feeds nothing but the optimiser; all of them run after the
         backward, between the two collectives of the step (see `_gemms_adiados`)."""
         ops = self.ops
-        a, b = ops.transpoe(gy), ops.transpoe(x)
-        if self.redutor is None:
-            self._grads[nome] = ops.gemm(a, b, cru=True)
-        else:
+        if self.redutor is not None:
+            a, b = ops.transpoe(gy), ops.transpoe(x)
             self._adiados.append((nome, a, b, ops.max_linha(a), ops.max_linha(b)))
+            return
+        if self._lado is None:
+            self._grads[nome] = ops.gemm(ops.transpoe(gy), ops.transpoe(x), cru=True)
+            return
+        # A weight gradient is a leaf of the backward graph: its two transpositions and its GEMM run on a second
+        # stream, next to the dX chain, and fill SMs the small GEMMs of that chain leave idle.  Under capture the
+        # second stream becomes a parallel branch of the CUDA graph.
+        principal = torch.cuda.current_stream()
+        self._lado.wait_stream(principal)
+        for t in (*gy, *x):
+            t.record_stream(self._lado)
+        with torch.cuda.stream(self._lado):
+            ops.lib.jt_stream(self._lado.cuda_stream)
+            try:
+                self._grads[nome] = ops.gemm(ops.transpoe(gy), ops.transpoe(x), cru=True)
+            finally:
+                ops.lib.jt_stream(principal.cuda_stream)
 
     def _gemms_adiados(self, maximos):
-        """Data parallel, after the MAX collective: every weight-gradient GEMM with the global row maxima."""
-        for (nome, a, b, _, _), (RA, RB) in zip(self._adiados, maximos):
+        """Data parallel, after the MAX collective: every weight-gradient GEMM with the global row maxima.  The GEMMs
+        are independent of each other, so on the GPU they are dealt round-robin to a few streams (parallel branches
+        of the CUDA graph when recording) and joined at the end."""
+        ops = self.ops
+        principal = torch.cuda.current_stream() if self._ramos else None
+        for r in self._ramos:
+            r.wait_stream(principal)
+        for i, ((nome, a, b, _, _), (RA, RB)) in enumerate(zip(self._adiados, maximos)):
             with self.reg.trecho(nome):
-                self._grads[nome] = self.ops.gemm(a, b, cru=True, RA=RA, RB=RB)
+                if not self._ramos:
+                    self._grads[nome] = ops.gemm(a, b, cru=True, RA=RA, RB=RB)
+                    continue
+                ramo = self._ramos[i % len(self._ramos)]
+                for t in (*a, *b, RA, RB):
+                    t.record_stream(ramo)
+                with torch.cuda.stream(ramo):
+                    ops.lib.jt_stream(ramo.cuda_stream)
+                    try:
+                        self._grads[nome] = ops.gemm(a, b, cru=True, RA=RA, RB=RB)
+                    finally:
+                        ops.lib.jt_stream(principal.cuda_stream)
+        for r in self._ramos:
+            principal.wait_stream(r)
         self._adiados = []
 
     def _otimiza(self, grads, k_lr):
@@ -93,6 +132,8 @@ class Modelo:
         if k_lr is None:
             return perda
         grads = self._grads
+        if self._lado is not None:
+            torch.cuda.current_stream().wait_stream(self._lado)          # join the weight-gradient branch
         if self.redutor is not None:
             with self.reg.trecho("gradientes de peso"):
                 self._gemms_adiados(self.redutor.maximos_tudo([(ra, rb) for _, _, _, ra, rb in self._adiados]))
