@@ -55,7 +55,7 @@ class Modelo:
         self.error_feedback = True
         self.estatisticas = False
         # second stream for the weight-gradient GEMMs (single GPU, CUDA launcher only)
-        usa_lado = redutor is None and hasattr(ops, "lib") and torch.device(dev).type == "cuda"
+        usa_lado = hasattr(ops, "lib") and torch.device(dev).type == "cuda"
         self._lado = torch.cuda.Stream(device=dev) if usa_lado else None
         na_gpu = redutor is not None and hasattr(ops, "lib") and torch.device(dev).type == "cuda"
         self._ramos = [torch.cuda.Stream(device=dev) for _ in range(3)] if na_gpu else []
@@ -71,12 +71,12 @@ class Modelo:
         maxima are kept - because a weight gradient feeds nothing but the optimiser; all of them run after the
         backward, between the two collectives of the step (see `_gemms_adiados`)."""
         ops = self.ops
-        if self.redutor is not None:
-            a, b = ops.transpoe(gy), ops.transpoe(x)
-            self._adiados.append((nome, a, b, ops.max_linha(a), ops.max_linha(b)))
-            return
         if self._lado is None:
-            self._grads[nome] = ops.gemm(ops.transpoe(gy), ops.transpoe(x), cru=True)
+            a, b = ops.transpoe(gy), ops.transpoe(x)
+            if self.redutor is None:
+                self._grads[nome] = ops.gemm(a, b, cru=True)
+            else:
+                self._adiados.append((nome, a, b, ops.max_linha(a), ops.max_linha(b)))
             return
         # A weight gradient is a leaf of the backward graph: its two transpositions and its GEMM run on a second
         # stream, next to the dX chain, and fill SMs the small GEMMs of that chain leave idle.  Under capture the
@@ -88,7 +88,11 @@ class Modelo:
         with torch.cuda.stream(self._lado):
             ops.lib.jt_stream(self._lado.cuda_stream)
             try:
-                self._grads[nome] = ops.gemm(ops.transpoe(gy), ops.transpoe(x), cru=True)
+                a, b = ops.transpoe(gy), ops.transpoe(x)
+                if self.redutor is None:
+                    self._grads[nome] = ops.gemm(a, b, cru=True)
+                else:       # data parallel: only the transpositions and the row maxima now, the GEMM after the exchange
+                    self._adiados.append((nome, a, b, ops.max_linha(a), ops.max_linha(b)))
             finally:
                 ops.lib.jt_stream(principal.cuda_stream)
 
@@ -132,8 +136,6 @@ class Modelo:
         if k_lr is None:
             return perda
         grads = self._grads
-        if self._lado is not None:
-            torch.cuda.current_stream().wait_stream(self._lado)          # join the weight-gradient branch
         if self.redutor is not None:
             with self.reg.trecho("gradientes de peso"):
                 self._gemms_adiados(self.redutor.maximos_tudo([(ra, rb) for _, _, _, ra, rb in self._adiados]))
@@ -206,6 +208,8 @@ class Modelo:
                         self._st(f"c{l}.grad_qkv", gq); self._st(f"c{l}.grad_residuo", gx)
             with reg.trecho("embedding"):
                 self._grad_peso("emb", ops.um_quente(tok, self.V), gx)
+        if self._lado is not None:
+            torch.cuda.current_stream().wait_stream(self._lado)          # join the weight-gradient branch
         return perda
 
 
