@@ -206,6 +206,96 @@ __global__ void __launch_bounds__(256) k_transpoe(const int8_t* __restrict__ X, 
     }
 }
 
+// Transposition for block 32, wide tiles: 128 rows x 256 columns per CTA.  A thread owns a 32-row block of 4
+// adjacent columns (one 32-bit word per row) and quantises the 4 new blocks without leaving its registers.
+// The quantiser runs in fp32, exactly: a mantissa times 2^(e - eref) is exact in fp32, the largest magnitude gives
+// top = max(e + bitlen(v)) through its exponent field, and one FFMA against 1.5*2^23 rounds v * 2^(e - E) half to
+// even (|result| <= 127, inside the window).  A transposed block can never need the "one more bit" retry
+// (|m| <= 127 going in).  Blocks whose exponents are more than 100 apart take an integer path.
+constexpr int T32_PW = 256 / 4 + 1;
+// integer path of k_transpoe32 for one column of a block whose exponents are too far apart for fp32 (cold)
+__device__ __noinline__ void transpoe32_lento(const uint32_t (*tile)[T32_PW], const int8_t (*et)[8], int rb, int cw, int k, int8_t* dst,
+                                              int8_t* Edst, int kid, long long idx0) {
+    int v[32], e[32], q[32];
+#pragma unroll
+    for (int i = 0; i < 32; i++) {
+        v[i] = (int)(int8_t)(tile[rb * 32 + i][cw] >> (8 * k));
+        e[i] = et[rb * 32 + i][cw >> 3];
+    }
+    const int Eo = quant_geral<32, 1>(v, e, q, kid, idx0);
+#pragma unroll
+    for (int i4 = 0; i4 < 8; i4++) reinterpret_cast<uint32_t*>(dst)[i4] = junta4(q[4 * i4], q[4 * i4 + 1], q[4 * i4 + 2], q[4 * i4 + 3]);
+    *Edst = (int8_t)Eo;
+}
+
+__global__ void __launch_bounds__(256, 2) k_transpoe32(const int8_t* __restrict__ X, const int8_t* __restrict__ EX, int8_t* __restrict__ Y,
+                                                       int8_t* __restrict__ EY, int R, int C, int kid) {
+    constexpr int TR = 128, TC = 256, PW = T32_PW;
+    __shared__ uint32_t tile[TR][PW];
+    __shared__ __align__(4) int8_t et[TR][8];
+    const int r0 = blockIdx.y * TR, c0 = blockIdx.x * TC;
+    const int tid = threadIdx.x, wp = tid >> 5, lane = tid & 31;
+    const int nbx = C / 32, nby = R / 32;
+#pragma unroll
+    for (int k = 0; k < 8; k++) {
+        const int idx = tid + 256 * k, lr = idx >> 4, c16 = idx & 15;
+        const uint4 v = *reinterpret_cast<const uint4*>(X + (size_t)(r0 + lr) * C + c0 + c16 * 16);
+        tile[lr][c16 * 4] = v.x; tile[lr][c16 * 4 + 1] = v.y; tile[lr][c16 * 4 + 2] = v.z; tile[lr][c16 * 4 + 3] = v.w;
+    }
+    {
+        const int lr = tid >> 1, k4 = (tid & 1) * 4;
+        *reinterpret_cast<uint32_t*>(&et[lr][k4]) = *reinterpret_cast<const uint32_t*>(EX + (size_t)(r0 + lr) * nbx + c0 / 32 + k4);
+    }
+    __syncthreads();
+    const int rb = wp >> 1, cw = lane + 32 * (wp & 1);              // 32-row block, word column
+    uint32_t w[32];
+    float A[32];
+    int eref = -128, emin = 127;
+#pragma unroll
+    for (int i = 0; i < 32; i++) {
+        w[i] = tile[rb * 32 + i][cw];
+        const int e = et[rb * 32 + i][cw >> 3];
+        eref = max(eref, e);
+        if (w[i]) emin = min(emin, e);
+    }
+#pragma unroll
+    for (int i = 0; i < 32; i++) A[i] = __int_as_float(max(127 + (int)et[rb * 32 + i][cw >> 3] - eref, 0) << 23);
+    const bool largo = eref - emin > 100;                           // spread too wide for the fp32 path
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+        const size_t col = (size_t)(c0 + 4 * cw + k);
+        int8_t* dst = Y + col * R + r0 + rb * 32;
+        int8_t* Edst = EY + col * nby + (r0 + rb * 32) / 32;
+        if (largo) {
+            transpoe32_lento(tile, et, rb, cw, k, dst, Edst, kid, (long long)col * R + r0 + rb * 32);
+            continue;
+        }
+        float t[32], mx = 0.f;
+#pragma unroll
+        for (int i = 0; i < 32; i++) {
+            t[i] = (float)(int)(int8_t)(w[i] >> (8 * k)) * A[i];
+            mx = fmaxf(mx, fabsf(t[i]));
+        }
+        const int expo = (__float_as_int(mx) >> 23) - 127;          // floor(log2 mx); mx is a normal number or 0 here
+        int Eo = eref + expo + 1 - 7;
+        const bool morto = mx == 0.f || Eo < -126;
+        if (!morto && Eo > 126) reporta(E_EXP, kid, (long long)col * R + r0 + rb * 32, Eo, eref);
+        const float B = morto ? 0.f : __int_as_float((127 + 6 - expo) << 23);
+        if (morto) Eo = E_ZERO;
+        uint32_t saida[8];
+#pragma unroll
+        for (int i4 = 0; i4 < 8; i4++) {
+            uint32_t r[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++) r[j] = (uint32_t)__float_as_int(fmaf(t[4 * i4 + j], B, 12582912.0f));
+            saida[i4] = __byte_perm(__byte_perm(r[0], r[1], 0x0040), __byte_perm(r[2], r[3], 0x0040), 0x5410);
+        }
+        reinterpret_cast<uint4*>(dst)[0] = make_uint4(saida[0], saida[1], saida[2], saida[3]);
+        reinterpret_cast<uint4*>(dst)[1] = make_uint4(saida[4], saida[5], saida[6], saida[7]);
+        *Edst = (int8_t)Eo;
+    }
+}
+
 // RMSNorm without gain, one warp per row, NP*512 >= D columns held in registers.  ops.py:153-165
 //   ss = sum_b rnd(sq_b << G, 2 (emax - e_b));  r = isqrt(ss >> log2D);  k = bitlen(r) + 10;  inv = 2^k / r
 //   y = quant(x * inv, e_b - k - emax + G/2);  cache = (r, emax)

@@ -226,6 +226,10 @@ int jt_peso(void* Wm, void* WE, const void* Mm, const void* ME, void* Rm, void* 
 }
 int jt_transpoe(const void* X, const void* EX, void* Y, void* EY, int R, int C, int kid) {
     if (R <= 0 || C <= 0 || R % 128 || C % 64 || C % g_blk) return (int)cudaErrorInvalidValue;
+    if (g_blk == 32 && C % 256 == 0 && ((uintptr_t)EX & 3) == 0) {
+        k_transpoe32<<<dim3(C / 256, R / 128), 256, 0, g_stream>>>((const int8_t*)X, (const int8_t*)EX, (int8_t*)Y, (int8_t*)EY, R, C, kid);
+        return fim();
+    }
     const dim3 grade(C / 64, R / 128);
     if (g_blk == 32) k_transpoe<32><<<grade, 256, 0, g_stream>>>((const int8_t*)X, (const int8_t*)EX, (int8_t*)Y, (int8_t*)EY, R, C, kid);
     else k_transpoe<128><<<grade, 256, 0, g_stream>>>((const int8_t*)X, (const int8_t*)EX, (int8_t*)Y, (int8_t*)EY, R, C, kid);

@@ -241,3 +241,17 @@ def test_atencao_generalizada(amb, blk, Bt, T, H, D, limite):
         ops.ATENCAO_LIMITE = False
     compara(f"atencao {blk}/{Bt}/{T}/{H}/{D}", [*o_c, P_c], [*o_r, P_r])
     compara(f"atencao_back {blk}/{Bt}/{T}/{H}/{D} limite={limite}", list(g_c), list(g_r))
+
+
+@pytest.mark.parametrize("R,C,esp,zera", [(256, 512, 4, 0.0), (128, 1024, 12, 0.1), (384, 256, 60, 0.3), (128, 256, 0, 0.0), (256, 768, 25, 0.5)])
+def test_transpoe_largo(amb, R, C, esp, zera):
+    """The wide-tile block-32 transposition (fp32 exact quantiser) against the oracle, including exponent spreads
+    beyond what fp32 can align (integer path) and mostly-zero tensors."""
+    ops, oc, reg = amb
+    ops.define_blk(32)
+    reg.novo_passo(0)
+    G = casos.Gen(4000 + R + C + esp, 32)
+    X = G.bloco(R, C, espalha=esp, zera=zera, e0=-5)
+    out = oc.transpoe(para_gpu(X))
+    torch.cuda.synchronize()
+    compara(f"transpoe {R}x{C} esp {esp}", list(out), list(spec.Spec(32).transpoe(X)))
