@@ -91,6 +91,9 @@ int jt_blk_atual(void);
 /* GEMM path: 0 automatic | 1 tensor cores with FFMA rounding (block 32; exact while every K-block product stays
  * below 2^18) | 2 CUDA cores (dp4a) | 3 tensor cores with cvt rounding (what 0 selects when the shape allows). */
 int jt_gemm_via(int via);
+/* Tile width of the tensor-core GEMM: 0 automatic (64 columns when 128-column tiles would leave most SMs idle, block
+ * 32 only) | 64 | 128. */
+int jt_gemm_tn(int tn);
 /* jt_gemm_f with optional externally supplied row-maximum exponents RA[M], RB[N] (int8).  A data-parallel rank
  * passes the maxima over all ranks, so that the int32 partial sums of all ranks share one exponent and their
  * integer sum equals the single-GPU result (the reference's split-K argument, jatai_cuda.cu:214-216). */

@@ -21,23 +21,26 @@ struct SaidaGemm {
 };
 
 // Called by NTH threads (whole warps, `tid` in [0, NTH)) after the staged tile is visible to all of them.
-// Task = 16 consecutive columns of one row.  Within a warp lane l takes row (l % 4) and chunk (l / 4) of a
-// 4-row group, so the 8 lanes of a shared-memory phase read different rows (no bank conflict) while the 8
-// lanes that share l % 4 still write 128 contiguous bytes; the lanes of one exponent block sit 4 apart.
-template <int BLK, int MODO, int NTH>
+// Task = 16 consecutive columns of one row.  Within a warp lane l takes row (l % RPW) and chunk (l / RPW) of a
+// group of RPW rows (4 rows of a 128-column tile, 8 of a 64-column one), so the 8 lanes of a shared-memory phase
+// read different rows (no bank conflict) while the lanes that share a row still write contiguous bytes; the
+// lanes of one exponent block sit RPW apart.
+template <int BLK, int MODO, int NTH, int TNv = TN>
 __device__ __forceinline__ void epilogo_tile(const int* acc_s, const int* RAs, const int* RBs, int linhas, int m0, int n0, int N,
                                              const SaidaGemm& S, bool atomico, bool grava_e, int kid, int tid) {
     constexpr int GL = BLK / 16;
+    constexpr int RPW = 512 / TNv;             // rows a warp handles per iteration: 32 lanes / (TNv / 16) chunks per row
+    constexpr int PITCHv = TNv + 4;
     const int lane = tid & 31, wp = tid >> 5;
     const int nW = NTH / 32;
-    for (int g4 = wp; g4 < linhas / 4; g4 += nW) {
-        const int r = g4 * 4 + (lane & 3), ch = lane >> 2;
+    for (int g4 = wp; g4 < linhas / RPW; g4 += nW) {
+        const int r = g4 * RPW + (lane & (RPW - 1)), ch = lane / RPW;
         const int gi = m0 + r, gj = n0 + ch * 16;
         const long long o = (long long)gi * N + gj;
         int v[16];
 #pragma unroll
         for (int k = 0; k < 4; k++) {
-            const int4 w = *reinterpret_cast<const int4*>(acc_s + r * PITCH + ch * 16 + 4 * k);
+            const int4 w = *reinterpret_cast<const int4*>(acc_s + r * PITCHv + ch * 16 + 4 * k);
             v[4 * k] = w.x; v[4 * k + 1] = w.y; v[4 * k + 2] = w.z; v[4 * k + 3] = w.w;
         }
         const int ra = RAs[r] - GG;
@@ -64,7 +67,7 @@ __device__ __forceinline__ void epilogo_tile(const int* acc_s, const int* RAs, c
         int e[16], q[16];
 #pragma unroll
         for (int k = 0; k < 16; k++) e[k] = ra + RBs[ch * 16 + k];
-        const int E = quant_geral<16, GL, 4>(v, e, q, kid, o);
+        const int E = quant_geral<16, GL, RPW>(v, e, q, kid, o);
         const bool lider = (ch % GL) == 0;
         const long long oe = (long long)gi * (N / BLK) + gj / BLK;
         if (MODO == 0) {
@@ -76,7 +79,7 @@ __device__ __forceinline__ void epilogo_tile(const int* acc_s, const int* RAs, c
             const int ex = S.XE[oe], ec = max(ex, E) - 21;
 #pragma unroll
             for (int k = 0; k < 16; k++) x[k] = desloca(x[k], ec - ex) + desloca(q[k], ec - E);
-            const int E2 = quant_uniforme<16, GL, 4>(x, ec, z, kid, o);
+            const int E2 = quant_uniforme<16, GL, RPW>(x, ec, z, kid, o);
             grava16(S.Cm + o, z);
             if (lider) S.CE[oe] = (int8_t)E2;
         } else if (MODO == 3) {            // h and relu2(h): ops.py:134-137
@@ -85,7 +88,7 @@ __device__ __forceinline__ void epilogo_tile(const int* acc_s, const int* RAs, c
             int a[16], z[16];
 #pragma unroll
             for (int k = 0; k < 16; k++) { const int rr = max(q[k], 0); a[k] = rr * rr; }
-            const int E2 = quant_uniforme<16, GL, 4>(a, 2 * E, z, kid, o);
+            const int E2 = quant_uniforme<16, GL, RPW>(a, 2 * E, z, kid, o);
             grava16(S.Om2 + o, z);
             if (lider) S.OE2[oe] = (int8_t)E2;
         } else {                            // relu2_back(gemm, h): ops.py:139-141
@@ -94,7 +97,7 @@ __device__ __forceinline__ void epilogo_tile(const int* acc_s, const int* RAs, c
             const int eh = S.XE[oe];
 #pragma unroll
             for (int k = 0; k < 16; k++) h[k] = q[k] * max(h[k], 0) * 2;
-            const int E2 = quant_uniforme<16, GL, 4>(h, E + eh, z, kid, o);
+            const int E2 = quant_uniforme<16, GL, RPW>(h, E + eh, z, kid, o);
             grava16(S.Cm + o, z);
             if (lider) S.CE[oe] = (int8_t)E2;
         }

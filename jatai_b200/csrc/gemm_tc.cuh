@@ -25,15 +25,25 @@
 namespace jt {
 namespace tc {
 
-constexpr int TM = 128, KC = 128, NST = 4, NTM = 4, NTB = 4, N_DW = 16, N_EPI = N_DW * 32, N_THR = 64 + N_EPI;
-constexpr uint32_t A_BYTES = TM * KC, B_BYTES = TN * KC, STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr uint32_t OFF_ACC = NST * STAGE_BYTES;
-constexpr uint32_t OFF_TAB = OFF_ACC + TM * PITCH * 4;                  // scale table ring: [NTB][4][TN] floats
-constexpr uint32_t OFF_RA = OFF_TAB + NTB * 4 * TN * 4;
-constexpr uint32_t OFF_RB = OFF_RA + TM * 4;
-constexpr uint32_t OFF_BAR = OFF_RB + TN * 4;
-constexpr uint32_t OFF_MISC = OFF_BAR + (2 * NST + 2 * NTM + 2 * NTB) * 8;
-constexpr uint32_t SMEM_BYTES = OFF_MISC + 16 + 1024;          // + slack to align the base to 1024 bytes
+constexpr int TM = 128, KC = 128, NST = 4, NTM = 4, NTB = 4;
+constexpr uint32_t A_BYTES = TM * KC;
+// everything that depends on the tile width TNv (columns of C per CTA): 128, or 64 for shapes whose 128-wide tiling
+// would leave most SMs without a CTA (block 32 only: a 128-column exponent block does not fit a 64-column tile)
+template <int TNv>
+struct Cfg {
+    static constexpr int N_DW = TNv / 8;                       // drain warps: 4 lane quarters x (TNv / 32) column groups
+    static constexpr int N_EPI = N_DW * 32, N_THR = 64 + N_EPI, PITCHv = TNv + 4;
+    static constexpr uint32_t B_BYTES = TNv * KC, STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr uint32_t OFF_ACC = NST * STAGE_BYTES;
+    static constexpr uint32_t OFF_TAB = OFF_ACC + TM * PITCHv * 4;          // scale table ring: [NTB][4][TNv] floats
+    static constexpr uint32_t OFF_RA = OFF_TAB + NTB * 4 * TNv * 4;
+    static constexpr uint32_t OFF_RB = OFF_RA + TM * 4;
+    static constexpr uint32_t OFF_BAR = OFF_RB + TNv * 4;
+    static constexpr uint32_t OFF_MISC = OFF_BAR + (2 * NST + 2 * NTM + 2 * NTB) * 8;
+    static constexpr uint32_t SMEM_BYTES = OFF_MISC + 16 + 1024;            // + slack to align the base to 1024 bytes
+    // instruction descriptor kind::i8: D = s32, A = B = s8, both K-major, N = TNv, M = 128
+    static constexpr uint32_t IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TNv >> 3) << 17) | ((uint32_t)(TM >> 4) << 24);
+};
 constexpr long long LIMITE_CICLOS = 4000000000LL;              // ~2 s at B200 clocks
 constexpr uint32_t MAGIA = 0x4B400000u;                        // bit pattern of 1.5 * 2^23
 constexpr float MAGIA_F = 12582912.0f;
@@ -90,8 +100,6 @@ __device__ __forceinline__ void tc_mma_i8(uint32_t d_tmem, uint64_t da, uint64_t
 __device__ __forceinline__ uint64_t desc_sw128(uint32_t addr) {
     return (uint64_t)((addr >> 4) & 0x3FFF) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
 }
-// instruction descriptor kind::i8: D = s32, A = B = s8, both K-major, N = 128, M = 128
-constexpr uint32_t IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(TM >> 4) << 24);
 
 #define JT_O4(a, i) "=r"(a[i]), "=r"(a[i + 1]), "=r"(a[i + 2]), "=r"(a[i + 3])
 #define JT_O16(a, i) JT_O4(a, i), JT_O4(a, i + 4), JT_O4(a, i + 8), JT_O4(a, i + 12)
@@ -111,12 +119,17 @@ __device__ __forceinline__ float pot2(int e) { return __int_as_float((127 + e) <
 
 // VIA 0: round with one FFMA against 1.5*2^23 and add the bit pattern (valid while |p * 2^(4-s)| < 2^22);
 // VIA 1: exact float product, cvt.rni to int (valid for every input).
-template <int BLK, int MODO, int VIA>
-__global__ void __launch_bounds__(N_THR, 1) k_gemm_tc(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
+template <int BLK, int MODO, int VIA, int TNv>
+__global__ void __launch_bounds__(Cfg<TNv>::N_THR, 1) k_gemm_tc(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                                                       const int8_t* __restrict__ EA, const int8_t* __restrict__ EB,
                                                       const int8_t* __restrict__ RAg, const int8_t* __restrict__ RBg, SaidaGemm S, int M, int N,
                                                       int K, int pedacos_por_parte, int kid) {
     constexpr int NQ = KC / BLK;                 // K-blocks per 128-byte chunk: 4 (BLK 32) or 1 (BLK 128)
+    using C_ = Cfg<TNv>;
+    constexpr int N_DW = C_::N_DW, N_EPI = C_::N_EPI, PITCHv = C_::PITCHv;
+    constexpr uint32_t STAGE_BYTES = C_::STAGE_BYTES, OFF_ACC = C_::OFF_ACC, OFF_TAB = C_::OFF_TAB, OFF_RA = C_::OFF_RA, OFF_RB = C_::OFF_RB,
+                       OFF_BAR = C_::OFF_BAR, OFF_MISC = C_::OFF_MISC, IDESC = C_::IDESC;
+    static_assert(TNv == 128 || (TNv == 64 && BLK == 32), "64-column tiles exist for block 32 only");
     extern __shared__ unsigned char smem_bruto[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_bruto + 1023) & ~(uintptr_t)1023);
     const uint32_t sbase = smem_u32(smem);
@@ -130,7 +143,7 @@ __global__ void __launch_bounds__(N_THR, 1) k_gemm_tc(const __grid_constant__ CU
     volatile int* aborta = reinterpret_cast<volatile int*>(smem + OFF_MISC + 4);
 
     const int tid = threadIdx.x, wid = tid >> 5, lane = tid & 31;
-    const int m0 = blockIdx.y * TM, n0 = blockIdx.x * TN;
+    const int m0 = blockIdx.y * TM, n0 = blockIdx.x * TNv;
     const int nb = K / BLK;
     const int ped0 = blockIdx.z * pedacos_por_parte;             // first 128-byte chunk of this CTA's K range
     const int nfatias = pedacos_por_parte * NQ;                  // drains (K-blocks) this CTA performs
@@ -143,7 +156,7 @@ __global__ void __launch_bounds__(N_THR, 1) k_gemm_tc(const __grid_constant__ CU
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (wid == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(NTM * TN) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(NTM * TNv) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tc_fence_antes();
@@ -153,11 +166,12 @@ __global__ void __launch_bounds__(N_THR, 1) k_gemm_tc(const __grid_constant__ CU
 
     if (wid == 0) {
         // ------------------------------------------------------------------ TMA producer + column scale tables
-        // lane l owns columns l, l+32, l+64, l+96 of the tile: their row maxima RB and, per chunk, their scales
-        int RBc[4];
-        const int8_t* ebc[4];
+        // lane l owns columns l, l+32, ... of the tile: their row maxima RB and, per chunk, their scales
+        constexpr int NC = TNv / 32;
+        int RBc[NC];
+        const int8_t* ebc[NC];
 #pragma unroll
-        for (int k = 0; k < 4; k++) {
+        for (int k = 0; k < NC; k++) {
             const int col = lane + 32 * k;
             RBc[k] = RBg ? (int)RBg[n0 + col] : max_expoentes(EB + (size_t)(n0 + col) * nb, nb);
             RBs[col] = RBc[k];
@@ -177,18 +191,18 @@ __global__ void __launch_bounds__(N_THR, 1) k_gemm_tc(const __grid_constant__ CU
             ok = __all_sync(FULL, ok);
             if (!ok) break;
             const int sl = i % NTB;
-            uint32_t w[4];
+            uint32_t w[NC];
 #pragma unroll
-            for (int k = 0; k < 4; k++)
+            for (int k = 0; k < NC; k++)
                 w[k] = NQ == 4 ? *reinterpret_cast<const uint32_t*>(ebc[k] + 4 * i) : (uint32_t)(uint8_t)ebc[k][i];
             ok = __all_sync(FULL, espera(bar_bempty + 8 * sl, ((i / NTB) & 1) ^ 1, aborta, kid, 5));
             if (!ok) break;
 #pragma unroll
-            for (int k = 0; k < 4; k++)
+            for (int k = 0; k < NC; k++)
 #pragma unroll
                 for (int q = 0; q < NQ; q++) {
                     const int sb = min(RBc[k] - (int)(int8_t)(w[k] >> (8 * q)), 40);
-                    tabB[(sl * 4 + q) * TN + lane + 32 * k] = pot2(-sb);
+                    tabB[(sl * 4 + q) * TNv + lane + 32 * k] = pot2(-sb);
                 }
             mbar_arrive(bar_bfull + 8 * sl);
         }
@@ -208,7 +222,7 @@ __global__ void __launch_bounds__(N_THR, 1) k_gemm_tc(const __grid_constant__ CU
                         const int t = f % NTM;
                         if (!espera(bar_tempty + 8 * t, ((f / NTM) & 1) ^ 1, aborta, kid, 3)) { ok = false; break; }
                         tc_fence_depois();
-                        tc_mma_i8(tmem + t * TN, da + 2 * q, db + 2 * q, IDESC, 0);          // +32 bytes of K per instruction
+                        tc_mma_i8(tmem + t * TNv, da + 2 * q, db + 2 * q, IDESC, 0);          // +32 bytes of K per instruction
                         tc_commit(bar_tfull + 8 * t);
                     }
                 } else {
@@ -216,7 +230,7 @@ __global__ void __launch_bounds__(N_THR, 1) k_gemm_tc(const __grid_constant__ CU
                     if (!espera(bar_tempty + 8 * t, ((f / NTM) & 1) ^ 1, aborta, kid, 3)) break;
                     tc_fence_depois();
 #pragma unroll
-                    for (int q = 0; q < 4; q++) tc_mma_i8(tmem + t * TN, da + 2 * q, db + 2 * q, IDESC, q > 0);
+                    for (int q = 0; q < 4; q++) tc_mma_i8(tmem + t * TNv, da + 2 * q, db + 2 * q, IDESC, q > 0);
                     tc_commit(bar_tfull + 8 * t);
                     f++;
                 }
@@ -254,13 +268,13 @@ __global__ void __launch_bounds__(N_THR, 1) k_gemm_tc(const __grid_constant__ CU
                 if (!ok) break;
                 tc_fence_depois();
                 uint32_t d[32];
-                tmem_le32(tmem + ((uint32_t)(quarto * 32) << 16) + t * TN + cg * 32, d);
+                tmem_le32(tmem + ((uint32_t)(quarto * 32) << 16) + t * TNv + cg * 32, d);
                 tc_fence_antes();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_tempty + 8 * t);
                 const int sa = min(RA - (int)(int8_t)(eaw >> (8 * q)), 40);
                 const float fa = pot2(GG - sa), cneg = -MAGIA_F * fa;
-                const float4* tb = reinterpret_cast<const float4*>(tabB + (sl * 4 + q) * TN + cg * 32);
+                const float4* tb = reinterpret_cast<const float4*>(tabB + (sl * 4 + q) * TNv + cg * 32);
 #pragma unroll
                 for (int j4 = 0; j4 < 8; j4++) {
                     const float4 fb = tb[j4];
@@ -286,16 +300,16 @@ __global__ void __launch_bounds__(N_THR, 1) k_gemm_tc(const __grid_constant__ CU
         }
 #pragma unroll
         for (int j = 0; j < 32; j += 4)
-            *reinterpret_cast<int4*>(acc_s + lin * PITCH + cg * 32 + j) = make_int4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+            *reinterpret_cast<int4*>(acc_s + lin * PITCHv + cg * 32 + j) = make_int4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
         // the only barrier of the drain warps: reached by every drain thread exactly once, aborted or not
         asm volatile("bar.sync 1, %0;" ::"n"(N_EPI) : "memory");
-        epilogo_tile<BLK, MODO, N_EPI>(acc_s, RAs, RBs, TM, m0, n0, N, S, gridDim.z > 1, blockIdx.z == 0, kid, et);
+        epilogo_tile<BLK, MODO, N_EPI, TNv>(acc_s, RAs, RBs, TM, m0, n0, N, S, gridDim.z > 1, blockIdx.z == 0, kid, et);
     }
     tc_fence_antes();
     __syncthreads();
     if (wid == 1) {
         tc_fence_depois();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(NTM * TN) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(NTM * TNv) : "memory");
     }
 }
 

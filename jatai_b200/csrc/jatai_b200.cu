@@ -26,7 +26,8 @@ using namespace jt;
 static cudaStream_t g_stream = 0;
 static int g_blk = 32;               // exponent block length: 32 (native) or 128 (the reference's format)
 static int g_via = 0;                // GEMM path: 0 automatic | 1 tensor core, FFMA rounding | 2 CUDA cores | 3 tensor core, cvt rounding
-static int g_alvo_ctas = 148;        // split-K of raw GEMMs aims at this many CTAs
+static int g_alvo_ctas = 148;
+static int g_tn = 0;                 // tile width of the tensor-core GEMM: 0 automatic | 64 | 128        // split-K of raw GEMMs aims at this many CTAs
 
 static int fim() { return (int)cudaGetLastError(); }
 static unsigned nblocos16(long long n16) { return (unsigned)((n16 + 255) / 256); }
@@ -47,30 +48,31 @@ static PFN_tmap pega_tmap() {
     return g_tmap;
 }
 
-// 2-D map of an int8 matrix [linhas, K] (K contiguous): box = 128 rows x 128 bytes, 128-byte swizzle
-static bool faz_mapa(CUtensorMap* m, const void* p, int linhas, int K) {
+// 2-D map of an int8 matrix [linhas, K] (K contiguous): box = linhas_caixa rows x 128 bytes, 128-byte swizzle
+static bool faz_mapa(CUtensorMap* m, const void* p, int linhas, int K, int linhas_caixa = tc::TM) {
     PFN_tmap f = pega_tmap();
     if (!f) return false;
     cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)linhas};
     cuuint64_t passos[1] = {(cuuint64_t)K};
-    cuuint32_t caixa[2] = {(cuuint32_t)tc::KC, (cuuint32_t)tc::TM};
+    cuuint32_t caixa[2] = {(cuuint32_t)tc::KC, (cuuint32_t)linhas_caixa};
     cuuint32_t um[2] = {1, 1};
     return f(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(p), dims, passos, caixa, um, CU_TENSOR_MAP_INTERLEAVE_NONE,
              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int BLK, int MODO, int VIA>
+template <int BLK, int MODO, int VIA, int TNv>
 static int lanca_tc(const CUtensorMap& mA, const CUtensorMap& mB, const int8_t* EA, const int8_t* EB, const int8_t* RA, const int8_t* RB,
                     const SaidaGemm& S, int M, int N, int K, int partes, int kid) {
     static bool pronto = false;
-    auto k = tc::k_gemm_tc<BLK, MODO, VIA>;
+    using C_ = tc::Cfg<TNv>;
+    auto k = tc::k_gemm_tc<BLK, MODO, VIA, TNv>;
     if (!pronto) {
-        cudaError_t c = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc::SMEM_BYTES);
+        cudaError_t c = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C_::SMEM_BYTES);
         if (c != cudaSuccess) return (int)c;
         pronto = true;
     }
-    const dim3 grade(N / TN, M / tc::TM, partes);
-    k<<<grade, tc::N_THR, tc::SMEM_BYTES, g_stream>>>(mA, mB, EA, EB, RA, RB, S, M, N, K, (K / tc::KC) / partes, kid);
+    const dim3 grade(N / TNv, M / tc::TM, partes);
+    k<<<grade, C_::N_THR, C_::SMEM_BYTES, g_stream>>>(mA, mB, EA, EB, RA, RB, S, M, N, K, (K / tc::KC) / partes, kid);
     return fim();
 }
 
@@ -88,12 +90,18 @@ static int gemm_blk(const int8_t* A, const int8_t* EA, const int8_t* B, const in
     if (M <= 0 || N <= 0 || K <= 0 || M % 64 || N % TN || K % BLK || K % 32 || modo < 0 || modo > 4) return (int)cudaErrorInvalidValue;
     const bool alinhado = (((uintptr_t)A | (uintptr_t)B) & 15) == 0 && (((uintptr_t)EA | (uintptr_t)EB) & 3) == 0;
     bool usa_tc = g_via != 2 && M % tc::TM == 0 && K % tc::KC == 0 && alinhado;
+    // 64-column tiles (block 32 only) when they finish sooner: a 64-column tile costs ~0.55 of a 128-column one, and
+    // the GEMM takes ceil(tiles / 148) rounds of one CTA per SM
+    const long long tiles128 = (long long)(N / TN) * (M / tc::TM);
+    const double custo128 = (double)((tiles128 + 147) / 148), custo64 = 0.55 * (double)((2 * tiles128 + 147) / 148);
+    const bool estreito = BLK == 32 && usa_tc && g_tn != 128 && (g_tn == 64 || custo64 < custo128 - 0.01);
+    const int tn = estreito ? 64 : TN;
     CUtensorMap mA, mB;
-    if (usa_tc) usa_tc = faz_mapa(&mA, A, M, K) && faz_mapa(&mB, B, N, K);
+    if (usa_tc) usa_tc = faz_mapa(&mA, A, M, K) && faz_mapa(&mB, B, N, K, tn);
     if (!usa_tc && g_via != 0 && g_via != 2) return (int)cudaErrorInvalidValue;     // a forced tensor-core path never falls back silently
     // split-K (raw output only): powers of two while the grid stays below the target and the K range divides evenly
     const int unidades = usa_tc ? K / tc::KC : K / BLK;            // indivisible K units of the chosen kernel
-    const long long tiles = (long long)(N / TN) * (M / (usa_tc ? tc::TM : 64));
+    const long long tiles = usa_tc ? (long long)(N / tn) * (M / tc::TM) : (long long)(N / TN) * (M / 64);
     int partes = 1;
     if (modo == 1)
         while (partes * 2 <= unidades && tiles * partes * 2 <= g_alvo_ctas && unidades % (partes * 2) == 0) partes *= 2;
@@ -106,9 +114,13 @@ static int gemm_blk(const int8_t* A, const int8_t* EA, const int8_t* B, const in
 #define JT_TC(MD)                                                                                                    \
     case MD:                                                                                                         \
         if constexpr (BLK == 32) {                                                                                   \
-            if (g_via == 1) return lanca_tc<32, MD, 0>(mA, mB, EA, EB, RA, RB, S, M, N, K, partes, kid);             \
+            if (estreito) {                                                                                          \
+                if (g_via == 1) return lanca_tc<32, MD, 0, 64>(mA, mB, EA, EB, RA, RB, S, M, N, K, partes, kid);     \
+                return lanca_tc<32, MD, 1, 64>(mA, mB, EA, EB, RA, RB, S, M, N, K, partes, kid);                     \
+            }                                                                                                        \
+            if (g_via == 1) return lanca_tc<32, MD, 0, 128>(mA, mB, EA, EB, RA, RB, S, M, N, K, partes, kid);        \
         }                                                                                                            \
-        return lanca_tc<BLK, MD, 1>(mA, mB, EA, EB, RA, RB, S, M, N, K, partes, kid);
+        return lanca_tc<BLK, MD, 1, 128>(mA, mB, EA, EB, RA, RB, S, M, N, K, partes, kid);
         switch (modo) { JT_TC(0) JT_TC(1) JT_TC(2) JT_TC(3) JT_TC(4) }
 #undef JT_TC
     }
@@ -147,6 +159,11 @@ int jt_blk(int blk) {
     return 0;
 }
 int jt_blk_atual() { return g_blk; }
+int jt_gemm_tn(int tn) {
+    if (tn != 0 && tn != 64 && tn != 128) return (int)cudaErrorInvalidValue;
+    g_tn = tn;
+    return 0;
+}
 int jt_gemm_via(int via) {
     if (via < 0 || via > 3) return (int)cudaErrorInvalidValue;
     g_via = via;

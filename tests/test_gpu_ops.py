@@ -255,3 +255,25 @@ def test_transpoe_largo(amb, R, C, esp, zera):
     out = oc.transpoe(para_gpu(X))
     torch.cuda.synchronize()
     compara(f"transpoe {R}x{C} esp {esp}", list(out), list(spec.Spec(32).transpoe(X)))
+
+
+GEMMS32 = [(n, b, f) for n, b, f in casos.tabela(32) if "/gemm" in n]
+
+
+@pytest.mark.parametrize("tn", [64, 128])
+@pytest.mark.parametrize("nome,blk,f", GEMMS32, ids=[n for n, _, _ in GEMMS32])
+def test_gemm_largura_do_tile(amb, nome, blk, f, tn):
+    """Both tile widths of the tensor-core GEMM (64 and 128 columns), forced, on every GEMM case of the table."""
+    ops, oc, reg = amb
+    ops.define_blk(32)
+    oc.lib.jt_gemm_via(0)
+    assert oc.lib.jt_gemm_tn(tn) == 0
+    try:
+        reg.novo_passo(0)
+        G = casos.Gen(casos.semente(nome), blk)
+        op, args, kw = f(G)
+        outs = casos.roda(oc, op, tuple(para_gpu(a) for a in args), kw)
+        torch.cuda.synchronize()
+        compara(f"{nome} tn {tn}", outs, casos.roda(spec.Spec(blk), op, args, kw))
+    finally:
+        oc.lib.jt_gemm_tn(0)
