@@ -101,24 +101,39 @@ __device__ __forceinline__ void prod4x4(const int* a_s, const int* b_s, int ty, 
     }
 }
 
-// acc[r][k] += sum_{jj < nj} w_s[(4 ty + r) * WP + j0 + jj] * v_s[jj][lane + 32 k]     (k < ND, columns < HD)
+// Row products: out[r][d] = sum_j w_s[4 ty + r][j0 + j] * v_s[j][d] for the 4 rows of warp ty (P.V, dS'.k, dS'^T.q, P^T.dO).
+// A lane owns 4 adjacent columns d (d4 = lane % (HD/4)) and one of NJ = 32 / (HD/4) interleaved groups of 4 keys, so
+// both operands come in 128-bit shared-memory loads (4 rows x 4 keys of w, 4 keys x 4 columns of v -> 64 MACs per 8
+// loads); the NJ partial sums are added with shuffles at the end (acumula4_fim).  WP (pitch of w_s) is a multiple of 4.
 template <int HD>
-__device__ __forceinline__ void acumula_linhas(const int* w_s, int WP, const int* v_s, int j0, int nj, int ty, int lane,
-                                               int (&acc)[4][(HD + 31) / 32]) {
-    constexpr int PK = HD + 4, ND = (HD + 31) / 32;
-    if (lane >= HD) return;
-    const int* w0 = w_s + (4 * ty) * WP + j0;
-    for (int jj = 0; jj < nj; jj++) {
-        int w[4], v[ND];
+__device__ __forceinline__ void acumula4(const int* w_s, int WP, const int* v_s, int j0, int nj, int ty, int lane, int (&acc)[4][4]) {
+    constexpr int PK = HD + 4, ND4 = HD / 4, NJ = 32 / ND4;
+    const int d4 = lane % ND4, jsub = lane / ND4;
+    for (int jj = jsub * 4; jj < nj; jj += 4 * NJ) {
+        int4 w[4], v[4];
 #pragma unroll
-        for (int r = 0; r < 4; r++) w[r] = w0[r * WP + jj];
+        for (int r = 0; r < 4; r++) w[r] = *reinterpret_cast<const int4*>(w_s + (4 * ty + r) * WP + j0 + jj);
 #pragma unroll
-        for (int k = 0; k < ND; k++) v[k] = v_s[jj * PK + lane + 32 * k];
+        for (int c = 0; c < 4; c++) v[c] = *reinterpret_cast<const int4*>(v_s + (jj + c) * PK + 4 * d4);
+#pragma unroll
+        for (int r = 0; r < 4; r++) {
+            acc[r][0] += w[r].x * v[0].x + w[r].y * v[1].x + w[r].z * v[2].x + w[r].w * v[3].x;
+            acc[r][1] += w[r].x * v[0].y + w[r].y * v[1].y + w[r].z * v[2].y + w[r].w * v[3].y;
+            acc[r][2] += w[r].x * v[0].z + w[r].y * v[1].z + w[r].z * v[2].z + w[r].w * v[3].z;
+            acc[r][3] += w[r].x * v[0].w + w[r].y * v[1].w + w[r].z * v[2].w + w[r].w * v[3].w;
+        }
+    }
+}
+// adds the NJ partial sums; afterwards the lanes with lane < HD/4 hold columns 4 lane .. 4 lane + 3 of the 4 rows
+template <int HD>
+__device__ __forceinline__ void acumula4_fim(int (&acc)[4][4]) {
+    constexpr int ND4 = HD / 4;
+#pragma unroll
+    for (int o = 16; o >= ND4; o >>= 1)
 #pragma unroll
         for (int r = 0; r < 4; r++)
 #pragma unroll
-            for (int k = 0; k < ND; k++) acc[r][k] += w[r] * v[k];
-    }
+            for (int k = 0; k < 4; k++) acc[r][k] += __shfl_xor_sync(FULL, acc[r][k], o);
 }
 
 // CTA-wide maximum of a non-negative per-thread value -> one atomicMax
@@ -136,14 +151,14 @@ __device__ __forceinline__ void max_cta_atomico(int v, int* destino, int* red, i
 }
 
 // -------------------------------------------------------------------------------------------------- forward
-// ops.py:198-219.  grid (T/32, Bt*H), 256 threads.  Shared: u[32][T+1] int32, kv[128][hd+4], q[32][hd+4], pT[T][32] bytes.
+// ops.py:198-219.  grid (T/32, Bt*H), 256 threads.  Shared: u[32][T+4] int32, kv[128][hd+4], q[32][hd+4], pT[T][32] bytes.
 template <int HD>
 __global__ void __launch_bounds__(256) k_atencao(const int8_t* __restrict__ qm, const int8_t* __restrict__ qE, int* __restrict__ Oacc,
                                                  int16_t* __restrict__ Oe, uint8_t* __restrict__ P, int T, int H, int D, int GA, int blk, int lg2,
                                                  int kid) {
-    constexpr int PK = HD + 4, ND = (HD + 31) / 32;
+    constexpr int PK = HD + 4, ND4 = HD / 4;
     extern __shared__ __align__(16) int sm[];
-    const int TP = T + 1;
+    const int TP = T + 4;
     int* u_s = sm;
     int* kv_s = u_s + TI * TP;
     int* q_s = kv_s + TJ * PK;
@@ -208,27 +223,27 @@ __global__ void __launch_bounds__(256) k_atencao(const int8_t* __restrict__ qm, 
         *reinterpret_cast<uint4*>(P + ((size_t)bh * T + j) * T + i0 + hf * 16) = v;
     }
     // O = P . V
-    int o[4][ND];
+    int o[4][4];
 #pragma unroll
     for (int r = 0; r < 4; r++)
 #pragma unroll
-        for (int k = 0; k < ND; k++) o[r][k] = 0;
+        for (int k = 0; k < 4; k++) o[r][k] = 0;
     for (int j0 = 0; j0 < nproc; j0 += TJ) {
         __syncthreads();
         carrega_alinhado<HD>(kv_s, qm, qE, ld, blk, linha0, j0, TJ, T, 2 * D + h * HD, emv, GA, tid);
         __syncthreads();
-        acumula_linhas<HD>(u_s, TP, kv_s, j0, min(TJ, nproc - j0), ty, lane, o);
+        acumula4<HD>(u_s, TP, kv_s, j0, min(TJ, nproc - j0), ty, lane, o);
     }
-    if (lane < HD) {
+    acumula4_fim<HD>(o);
+    if (lane < ND4) {
         const int eo = (emv - GA) - 8;
+        const uint32_t e2 = (uint32_t)(eo & 0xffff) | ((uint32_t)eo << 16);
 #pragma unroll
-        for (int r = 0; r < 4; r++)
-#pragma unroll
-            for (int k = 0; k < ND; k++) {
-                const size_t p = (size_t)(linha0 + i0 + 4 * ty + r) * D + h * HD + lane + 32 * k;
-                Oacc[p] = o[r][k];
-                Oe[p] = (int16_t)eo;
-            }
+        for (int r = 0; r < 4; r++) {
+            const size_t p = (size_t)(linha0 + i0 + 4 * ty + r) * D + h * HD + 4 * lane;
+            *reinterpret_cast<int4*>(Oacc + p) = make_int4(o[r][0], o[r][1], o[r][2], o[r][3]);
+            *reinterpret_cast<uint2*>(Oe + p) = make_uint2(e2, e2);
+        }
     }
 }
 
@@ -276,10 +291,10 @@ __global__ void __launch_bounds__(256) k_lim(ArgsTras A) {
 // FASE 1: max |gP| over j <= i.   FASE 2: gP', s_lin, maxima.   FASE 3: dS', gq.     grid (T/32, Bt*H)
 template <int HD, int FASE>
 __global__ void __launch_bounds__(256) k_ab_linhas(ArgsTras A) {
-    constexpr int PK = HD + 4, ND = (HD + 31) / 32;
+    constexpr int PK = HD + 4, ND4 = HD / 4;
     extern __shared__ __align__(16) int sm[];
-    const int T = A.T, H = A.H, D = A.D, GA = A.GA, blk = A.blk, TP = T + 1;
-    int* g_s = sm;                                  // [32][T+1]: gP', then dS'
+    const int T = A.T, H = A.H, D = A.D, GA = A.GA, blk = A.blk, TP = T + 4;
+    int* g_s = sm;                                  // [32][T+4]: gP', then dS'
     int* b_s = g_s + (FASE == 1 ? 0 : TI * TP);     // [128][PK]: v chunk, then k chunk
     int* a_s = b_s + TJ * PK;                       // [32][PK]: dO tile
     uint8_t* pT = reinterpret_cast<uint8_t*>(a_s + TI * PK);      // [T][32]
@@ -357,42 +372,42 @@ __global__ void __launch_bounds__(256) k_ab_linhas(ArgsTras A) {
         for (int j = lane; j < nproc; j += 32) gr[j] = rnd_d((int)pT[j * TI + 4 * ty + r] * (gr[j] - sl), sh2);
     }
     const int emk = max_cabeca<HD>(A.qE, 3 * D / blk, blk, linha0, T, D + h * HD, red, tid);
-    int o[4][ND];
+    int o[4][4];
 #pragma unroll
     for (int r = 0; r < 4; r++)
 #pragma unroll
-        for (int k = 0; k < ND; k++) o[r][k] = 0;
+        for (int k = 0; k < 4; k++) o[r][k] = 0;
     for (int j0 = 0; j0 < nproc; j0 += TJ) {
         __syncthreads();
         carrega_alinhado<HD>(b_s, A.qm, A.qE, 3 * D, blk, linha0, j0, TJ, T, D + h * HD, emk, GA, tid);
         __syncthreads();
-        acumula_linhas<HD>(g_s, TP, b_s, j0, min(TJ, nproc - j0), ty, lane, o);
+        acumula4<HD>(g_s, TP, b_s, j0, min(TJ, nproc - j0), ty, lane, o);
     }
-    if (lane < HD) {
+    acumula4_fim<HD>(o);
+    if (lane < ND4) {
         const int eds = (emg - GA) + (emv - GA) + sh - 9 + sh2;
         const int e = eds + (emk - GA);
+        const uint32_t e2 = (uint32_t)(e & 0xffff) | ((uint32_t)e << 16);
 #pragma unroll
-        for (int r = 0; r < 4; r++)
-#pragma unroll
-            for (int k = 0; k < ND; k++) {
-                const size_t p = (size_t)(linha0 + i0 + 4 * ty + r) * 3 * D + h * HD + lane + 32 * k;
-                A.Gacc[p] = o[r][k];
-                A.Ge[p] = (int16_t)e;
-            }
+        for (int r = 0; r < 4; r++) {
+            const size_t p = (size_t)(linha0 + i0 + 4 * ty + r) * 3 * D + h * HD + 4 * lane;
+            *reinterpret_cast<int4*>(A.Gacc + p) = make_int4(o[r][0], o[r][1], o[r][2], o[r][3]);
+            *reinterpret_cast<uint2*>(A.Ge + p) = make_uint2(e2, e2);
+        }
     }
 }
 
 // key tiles: gk[j] = sum_i dS'[i][j] q[i], gv[j] = sum_i P[i][j] dO[i].   grid (T/32, Bt*H)
 template <int HD>
 __global__ void __launch_bounds__(256) k_ab_colunas(ArgsTras A) {
-    constexpr int PK = HD + 4, ND = (HD + 31) / 32, CP = TJ + 1;
+    constexpr int PK = HD + 4, ND4 = HD / 4, CP = TJ + 4;
     extern __shared__ __align__(16) int sm[];
     const int T = A.T, H = A.H, D = A.D, GA = A.GA, blk = A.blk;
     int* a_s = sm;                    // [32][PK]  v tile (keys of this CTA)
     int* b_s = a_s + TI * PK;         // [128][PK] dO chunk
     int* c_s = b_s + TJ * PK;         // [128][PK] q chunk
-    int* ds_c = c_s + TJ * PK;        // [32][129] dS' of the chunk
-    int* p_c = ds_c + TI * CP;        // [32][129] P of the chunk
+    int* ds_c = c_s + TJ * PK;        // [32][132] dS' of the chunk
+    int* p_c = ds_c + TI * CP;        // [32][132] P of the chunk
     __shared__ int red[8];
     const int tid = threadIdx.x, ty = tid >> 5, lane = tid & 31;
     const int bh = blockIdx.y, b = bh / H, h = bh % H, j0 = blockIdx.x * TI, linha0 = b * T;
@@ -402,11 +417,11 @@ __global__ void __launch_bounds__(256) k_ab_colunas(ArgsTras A) {
     const int emv = max_cabeca<HD>(A.qE, 3 * D / blk, blk, linha0, T, 2 * D + h * HD, red, tid);
     const int sh = desl1(est, A.limite), sh2 = desl2(est, A.limite);
     carrega_alinhado<HD>(a_s, A.qm, A.qE, 3 * D, blk, linha0, j0, TI, T, 2 * D + h * HD, emv, GA, tid);
-    int gk[4][ND], gv[4][ND];
+    int gk[4][4], gv[4][4];
 #pragma unroll
     for (int r = 0; r < 4; r++)
 #pragma unroll
-        for (int k = 0; k < ND; k++) gk[r][k] = gv[r][k] = 0;
+        for (int k = 0; k < 4; k++) gk[r][k] = gv[r][k] = 0;
     for (int ic = (j0 / TJ) * TJ; ic < T; ic += TJ) {
         __syncthreads();
         carrega_alinhado<HD>(b_s, A.gom, A.goE, D, blk, linha0, ic, TJ, T, h * HD, emg, GA, tid);
@@ -429,30 +444,31 @@ __global__ void __launch_bounds__(256) k_ab_colunas(ArgsTras A) {
             }
         __syncthreads();
         const int ni = min(TJ, T - ic);
-        acumula_linhas<HD>(ds_c, CP, c_s, 0, ni, ty, lane, gk);
-        acumula_linhas<HD>(p_c, CP, b_s, 0, ni, ty, lane, gv);
+        acumula4<HD>(ds_c, CP, c_s, 0, ni, ty, lane, gk);
+        acumula4<HD>(p_c, CP, b_s, 0, ni, ty, lane, gv);
     }
-    if (lane < HD) {
+    acumula4_fim<HD>(gk);
+    acumula4_fim<HD>(gv);
+    if (lane < ND4) {
         const int ego = emg - GA, eds = ego + (emv - GA) + sh - 9 + sh2;
         const int e_k = eds + (emq - GA), e_v = ego - 8;
+        const uint32_t k2 = (uint32_t)(e_k & 0xffff) | ((uint32_t)e_k << 16), v2 = (uint32_t)(e_v & 0xffff) | ((uint32_t)e_v << 16);
 #pragma unroll
-        for (int r = 0; r < 4; r++)
-#pragma unroll
-            for (int k = 0; k < ND; k++) {
-                const size_t p = (size_t)(linha0 + j0 + 4 * ty + r) * 3 * D + D + h * HD + lane + 32 * k;
-                A.Gacc[p] = gk[r][k];
-                A.Ge[p] = (int16_t)e_k;
-                A.Gacc[p + D] = gv[r][k];
-                A.Ge[p + D] = (int16_t)e_v;
-            }
+        for (int r = 0; r < 4; r++) {
+            const size_t p = (size_t)(linha0 + j0 + 4 * ty + r) * 3 * D + D + h * HD + 4 * lane;
+            *reinterpret_cast<int4*>(A.Gacc + p) = make_int4(gk[r][0], gk[r][1], gk[r][2], gk[r][3]);
+            *reinterpret_cast<uint2*>(A.Ge + p) = make_uint2(k2, k2);
+            *reinterpret_cast<int4*>(A.Gacc + p + D) = make_int4(gv[r][0], gv[r][1], gv[r][2], gv[r][3]);
+            *reinterpret_cast<uint2*>(A.Ge + p + D) = make_uint2(v2, v2);
+        }
     }
 }
 
-inline size_t smem_frente(int HD, int T) { return 4 * ((size_t)TI * (T + 1) + TJ * (HD + 4) + TI * (HD + 4)) + (size_t)T * TI; }
+inline size_t smem_frente(int HD, int T) { return 4 * ((size_t)TI * (T + 4) + TJ * (HD + 4) + TI * (HD + 4)) + (size_t)T * TI; }
 inline size_t smem_linhas(int HD, int T, int fase) {
-    return 4 * ((fase == 1 ? 0 : (size_t)TI * (T + 1)) + TJ * (HD + 4) + TI * (HD + 4)) + (size_t)T * TI;
+    return 4 * ((fase == 1 ? 0 : (size_t)TI * (T + 4)) + TJ * (HD + 4) + TI * (HD + 4)) + (size_t)T * TI;
 }
-inline size_t smem_colunas(int HD) { return 4 * ((size_t)TI * (HD + 4) + 2 * TJ * (HD + 4) + 2 * TI * (TJ + 1)); }
+inline size_t smem_colunas(int HD) { return 4 * ((size_t)TI * (HD + 4) + 2 * TJ * (HD + 4) + 2 * TI * (TJ + 4)); }
 
 }  // namespace at
 
