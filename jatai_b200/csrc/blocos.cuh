@@ -30,52 +30,182 @@ __global__ void __launch_bounds__(256) k_quant(const int* __restrict__ acc, cons
     if (lider) E[w] = (int8_t)Eo;
 }
 
-// z = x + y.  ops.py:128-132: ec = max(xE, yE) - 21; v = rnd(x, ec - xE) + rnd(y, ec - yE); quant(v, ec)
-template <int BLK>
+// ---- several 16-element chunks per thread --------------------------------------------------------------
+// A thread issues the 128-bit loads of U chunks (one every gridDim*blockDim chunks, so lane groups stay aligned)
+// before it touches any of them: with one chunk per thread the ~1300 resident threads of an SM keep only ~20 KB in
+// flight, far less than the ~45 KB that HBM latency x bandwidth asks for.
+#define JT_PEDACO(k)                                                                      \
+    const long long tk_ = t0_ + (long long)(k) * nth_;                                    \
+    const bool ativo = tk_ < n16;                                                         \
+    const long long t16 = ativo ? tk_ : 0;                                                \
+    const long long o = t16 * 16;                                                         \
+    const long long w = o / BLK;                                                          \
+    const bool lider = ativo && (t16 % (BLK / 16) == 0);
+#define JT_MULTI                                                                          \
+    const long long nth_ = (long long)gridDim.x * blockDim.x;                             \
+    const long long t0_ = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+
+__device__ __forceinline__ void bytes_para_float(const uint4& r, float (&f)[16]) {
+    const uint32_t u[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        f[4 * i + 0] = (float)(int)(int8_t)(u[i] & 0xff);
+        f[4 * i + 1] = (float)(int)(int8_t)((u[i] >> 8) & 0xff);
+        f[4 * i + 2] = (float)(int)(int8_t)((u[i] >> 16) & 0xff);
+        f[4 * i + 3] = (float)((int)u[i] >> 24);
+    }
+}
+
+// Block quantiser in fp32 for integer-valued floats below 2^24 that share the exponent e (exact: ops.py:58-72).
+// The largest magnitude gives bitlen through its exponent field; one FFMA against 1.5*2^23 rounds v * 2^-sh half
+// to even (the low byte of the result's bit pattern is the mantissa); the "one more bit" retry is decided on the
+// maximum alone, because rounding is monotone.  Returns E; `pac` receives the 16 mantissas.
+template <int GL, int ST = 1>
+__device__ __forceinline__ int quant_f32(const float (&f)[16], int e, uint4& pac, int kid, long long idx0, unsigned mask = FULL) {
+    float mx = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; i++) mx = fmaxf(mx, fabsf(f[i]));
+#pragma unroll
+    for (int o = GL / 2; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(mask, mx, o * ST));
+    const int expo = (__float_as_int(mx) >> 23) - 127;               // floor(log2 mx) for mx >= 1
+    int sh = expo - 6;                                               // bitlen - 7
+    float sc = __int_as_float((127 - sh) << 23);                     // 2^-sh
+    if ((__float_as_int(fmaf(mx, sc, 12582912.0f)) & 0x1ff) > 127) { sh += 1; sc *= 0.5f; }
+    const int E = e + sh;
+    if (mx == 0.f || E < -126) { pac = make_uint4(0, 0, 0, 0); return E_ZERO; }
+    if (E > 126) reporta(E_EXP, kid, idx0, E, e);
+    uint32_t r[16];
+#pragma unroll
+    for (int i = 0; i < 16; i++) r[i] = (uint32_t)__float_as_int(fmaf(f[i], sc, 12582912.0f));
+    pac.x = __byte_perm(__byte_perm(r[0], r[1], 0x0040), __byte_perm(r[2], r[3], 0x0040), 0x5410);
+    pac.y = __byte_perm(__byte_perm(r[4], r[5], 0x0040), __byte_perm(r[6], r[7], 0x0040), 0x5410);
+    pac.z = __byte_perm(__byte_perm(r[8], r[9], 0x0040), __byte_perm(r[10], r[11], 0x0040), 0x5410);
+    pac.w = __byte_perm(__byte_perm(r[12], r[13], 0x0040), __byte_perm(r[14], r[15], 0x0040), 0x5410);
+    return E;
+}
+
+// z = x + y.  ops.py:128-132: ec = max(xE, yE) - 21; v = rnd(x, ec - xE) + rnd(y, ec - yE); quant(v, ec).
+// With hi / lo = the operand of larger / smaller exponent and d their distance, v = 2^(21-dl) * w where dl = min(d, 21),
+// w = hi * 2^dl + lo' and lo' = lo (d <= 21) or rnd(lo, d - 21) (the specification rounds the far operand first).
+// The quantiser is invariant under the common power of two, so the block is quant(w, e_hi - dl): the same bits with
+// 28-bit instead of 30-bit intermediates, one code path for every d, and rounding shifts shared by the block.
+template <int BLK, int U = 4>
 __global__ void __launch_bounds__(256) k_soma(const int8_t* __restrict__ xm, const int8_t* __restrict__ xE, const int8_t* __restrict__ ym,
                                               const int8_t* __restrict__ yE, int8_t* __restrict__ zm, int8_t* __restrict__ zE,
                                               long long n16, int kid) {
-    JT_FIO16
-    int a[16], b[16], v[16], q[16];
-    le16(xm + o, a);
-    le16(ym + o, b);
-    const int ex = xE[w], ey = yE[w], ec = max(ex, ey) - 21;
-    const int sx = ec - ex, sy = ec - ey;          // >= -21: the left shifts stay below 2^28
+    constexpr int GL = BLK / 16;
+    JT_MULTI
+    uint4 rx[U], ry[U];
+    int ex[U], ey[U];
 #pragma unroll
-    for (int i = 0; i < 16; i++) v[i] = desloca(a[i], sx) + desloca(b[i], sy);
-    const int Eo = quant_uniforme<16, BLK / 16>(v, ec, q, kid, o);
-    if (ativo) grava16(zm + o, q);
-    if (lider) zE[w] = (int8_t)Eo;
+    for (int k = 0; k < U; k++) {
+        JT_PEDACO(k)
+        rx[k] = *reinterpret_cast<const uint4*>(xm + o);
+        ry[k] = *reinterpret_cast<const uint4*>(ym + o);
+        ex[k] = xE[w];
+        ey[k] = yE[w];
+        (void)lider;
+    }
+#pragma unroll
+    for (int k = 0; k < U; k++) {
+        JT_PEDACO(k)
+        const bool x_maior = ex[k] >= ey[k];
+        const int eH = x_maior ? ex[k] : ey[k], d = x_maior ? ex[k] - ey[k] : ey[k] - ex[k];
+        const int dl = min(d, 21), s2 = d - dl;                         // s2 > 0: the far operand is rounded first
+        int hi[16], lo[16], wv[16];
+        desempacota16(x_maior ? rx[k] : ry[k], hi);
+        desempacota16(x_maior ? ry[k] : rx[k], lo);
+        int mx = 0;
+#pragma unroll
+        for (int i = 0; i < 16; i++) {
+            wv[i] = (hi[i] << dl) + rnd_d(lo[i], s2);
+            mx = max(mx, wv[i] < 0 ? -wv[i] : wv[i]);
+        }
+        mx = grupo_max<GL>(mx);
+        int s = bitlen(mx) - 7;
+        if (desloca(mx, s) > 127) s += 1;
+        const int E = eH - dl + s;
+        uint4 pac = make_uint4(0, 0, 0, 0);
+        int Eo = E_ZERO;
+        if (mx != 0 && E >= -126) {
+            if (E > 126) reporta(E_EXP, kid, o, E, eH);
+            Eo = E;
+            int q[16];
+            if (s > 0) {
+                const int c = (1 << (s - 1)) - 1;
+#pragma unroll
+                for (int i = 0; i < 16; i++) q[i] = (wv[i] + c + ((wv[i] >> s) & 1)) >> s;
+            } else {
+#pragma unroll
+                for (int i = 0; i < 16; i++) q[i] = wv[i] << (-s);
+            }
+            pac.x = junta4(q[0], q[1], q[2], q[3]);
+            pac.y = junta4(q[4], q[5], q[6], q[7]);
+            pac.z = junta4(q[8], q[9], q[10], q[11]);
+            pac.w = junta4(q[12], q[13], q[14], q[15]);
+        }
+        if (ativo) *reinterpret_cast<uint4*>(zm + o) = pac;
+        if (lider) zE[w] = (int8_t)Eo;
+    }
 }
 
-// a = max(h, 0)^2.  ops.py:134-137
-template <int BLK>
+// a = max(h, 0)^2.  ops.py:134-137.  fp32 path: h^2 <= 16129 is exact
+template <int BLK, int U = 4>
 __global__ void __launch_bounds__(256) k_relu2(const int8_t* __restrict__ hm, const int8_t* __restrict__ hE, int8_t* __restrict__ am,
                                                int8_t* __restrict__ aE, long long n16, int kid) {
-    JT_FIO16
-    int h[16], v[16], q[16];
-    le16(hm + o, h);
+    JT_MULTI
+    uint4 rh[U];
+    int eh[U];
 #pragma unroll
-    for (int i = 0; i < 16; i++) { const int r = max(h[i], 0); v[i] = r * r; }
-    const int Eo = quant_uniforme<16, BLK / 16>(v, 2 * (int)hE[w], q, kid, o);
-    if (ativo) grava16(am + o, q);
-    if (lider) aE[w] = (int8_t)Eo;
+    for (int k = 0; k < U; k++) {
+        JT_PEDACO(k)
+        rh[k] = *reinterpret_cast<const uint4*>(hm + o);
+        eh[k] = hE[w];
+        (void)lider;
+    }
+#pragma unroll
+    for (int k = 0; k < U; k++) {
+        JT_PEDACO(k)
+        float f[16];
+        bytes_para_float(rh[k], f);
+#pragma unroll
+        for (int i = 0; i < 16; i++) { const float r = fmaxf(f[i], 0.f); f[i] = r * r; }
+        uint4 pac;
+        const int Eo = quant_f32<BLK / 16>(f, 2 * eh[k], pac, kid, o);
+        if (ativo) *reinterpret_cast<uint4*>(am + o) = pac;
+        if (lider) aE[w] = (int8_t)Eo;
+    }
 }
 
-// gh = g * 2 * max(h, 0).  ops.py:139-141
-template <int BLK>
+// gh = g * 2 * max(h, 0).  ops.py:139-141.  fp32 path: |g h 2| <= 32258 is exact
+template <int BLK, int U = 4>
 __global__ void __launch_bounds__(256) k_relu2_back(const int8_t* __restrict__ gm, const int8_t* __restrict__ gE, const int8_t* __restrict__ hm,
                                                     const int8_t* __restrict__ hE, int8_t* __restrict__ om, int8_t* __restrict__ oE,
                                                     long long n16, int kid) {
-    JT_FIO16
-    int g[16], h[16], v[16], q[16];
-    le16(gm + o, g);
-    le16(hm + o, h);
+    JT_MULTI
+    uint4 rg[U], rh[U];
+    int ee[U];
 #pragma unroll
-    for (int i = 0; i < 16; i++) v[i] = g[i] * max(h[i], 0) * 2;
-    const int Eo = quant_uniforme<16, BLK / 16>(v, (int)gE[w] + (int)hE[w], q, kid, o);
-    if (ativo) grava16(om + o, q);
-    if (lider) oE[w] = (int8_t)Eo;
+    for (int k = 0; k < U; k++) {
+        JT_PEDACO(k)
+        rg[k] = *reinterpret_cast<const uint4*>(gm + o);
+        rh[k] = *reinterpret_cast<const uint4*>(hm + o);
+        ee[k] = (int)gE[w] + (int)hE[w];
+        (void)lider;
+    }
+#pragma unroll
+    for (int k = 0; k < U; k++) {
+        JT_PEDACO(k)
+        float g[16], h[16];
+        bytes_para_float(rg[k], g);
+        bytes_para_float(rh[k], h);
+#pragma unroll
+        for (int i = 0; i < 16; i++) g[i] = g[i] * fmaxf(h[i], 0.f) * 2.f;
+        uint4 pac;
+        const int Eo = quant_f32<BLK / 16>(g, ee[k], pac, kid, o);
+        if (ativo) *reinterpret_cast<uint4*>(om + o) = pac;
+        if (lider) oE[w] = (int8_t)Eo;
+    }
 }
 
 // momentum, in place: m <- quant(rnd(7 m, ec - em) + rnd(g, ec - eg), ec), em = ME - 3,
@@ -341,15 +471,17 @@ __global__ void __launch_bounds__(256) k_rms(const int8_t* __restrict__ Xm, cons
     const int r = isqrt_i(ss >> log2D);
     const int k = bitlen(r) + 10;
     const int inv = (1 << k) / r;
+    const float invf = (float)inv;                   // inv <= 2^11 and |x| <= 127: x * inv < 2^18 is exact in fp32
 #pragma unroll
     for (int p = 0; p < NP; p++) {
-        int v[16], q[16];
+        float f[16];
 #pragma unroll
-        for (int i = 0; i < 16; i++) v[i] = x[p][i] * inv;
+        for (int i = 0; i < 16; i++) f[i] = (float)x[p][i] * invf;
         const int c = (p * 32 + lane) * 16;
-        const int Eo = quant_uniforme<16, GL>(v, eb[p] - k - emax + G / 2, q, kid, lin * D + c);
+        uint4 pac;
+        const int Eo = quant_f32<GL>(f, eb[p] - k - emax + G / 2, pac, kid, lin * D + c);
         if (tem[p] && linha_ok) {
-            grava16(Ym + lin * D + c, q);
+            *reinterpret_cast<uint4*>(Ym + lin * D + c) = pac;
             if ((lane % GL) == 0) YE[lin * nb + c / BLK] = (int8_t)Eo;
         }
     }

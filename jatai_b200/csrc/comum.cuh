@@ -83,14 +83,15 @@ __device__ __forceinline__ int isqrt_i(int n) {
 
 // ---------------------------------------------------------------------------------------- lane groups
 // GL lanes (a power of two) at lane distance ST cooperate on one exponent block.  All 32 lanes must call.
-template <int GL, int ST = 1> __device__ __forceinline__ int grupo_max(int v) {
+// `mask` names the lanes that execute the call together (whole groups); FULL unless the caller has branched.
+template <int GL, int ST = 1> __device__ __forceinline__ int grupo_max(int v, unsigned mask = FULL) {
 #pragma unroll
-    for (int o = GL / 2; o; o >>= 1) v = max(v, __shfl_xor_sync(FULL, v, o * ST));
+    for (int o = GL / 2; o; o >>= 1) v = max(v, __shfl_xor_sync(mask, v, o * ST));
     return v;
 }
-template <int GL, int ST = 1> __device__ __forceinline__ int grupo_or(int v) {
+template <int GL, int ST = 1> __device__ __forceinline__ int grupo_or(int v, unsigned mask = FULL) {
 #pragma unroll
-    for (int o = GL / 2; o; o >>= 1) v |= __shfl_xor_sync(FULL, v, o * ST);
+    for (int o = GL / 2; o; o >>= 1) v |= __shfl_xor_sync(mask, v, o * ST);
     return v;
 }
 __device__ __forceinline__ int warp_max(int v) { return grupo_max<32>(v); }
@@ -109,6 +110,16 @@ __device__ __forceinline__ long long warp_sum64(long long v) {
 // A thread of the bandwidth kernels owns 16 consecutive elements: one 128-bit access of int8 data.
 __device__ __forceinline__ void le16(const int8_t* p, int (&v)[16]) {
     const uint4 w = *reinterpret_cast<const uint4*>(p);
+    const uint32_t u[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        v[4 * i + 0] = (int)(int8_t)(u[i] & 0xff);
+        v[4 * i + 1] = (int)(int8_t)((u[i] >> 8) & 0xff);
+        v[4 * i + 2] = (int)(int8_t)((u[i] >> 16) & 0xff);
+        v[4 * i + 3] = (int)u[i] >> 24;
+    }
+}
+__device__ __forceinline__ void desempacota16(const uint4& w, int (&v)[16]) {
     const uint32_t u[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
     for (int i = 0; i < 4; i++) {
@@ -157,11 +168,11 @@ __device__ __forceinline__ void le16_i16(const int16_t* p, int (&v)[16]) {
 
 // all values share the exponent e: only the largest magnitude can overflow (rounding is monotone and odd)
 template <int NV, int GL, int ST = 1>
-__device__ __forceinline__ int quant_uniforme(const int (&v)[NV], int e, int (&q)[NV], int kid, long long idx0) {
+__device__ __forceinline__ int quant_uniforme(const int (&v)[NV], int e, int (&q)[NV], int kid, long long idx0, unsigned mask = FULL) {
     int mx = 0;
 #pragma unroll
     for (int i = 0; i < NV; i++) mx = max(mx, v[i] < 0 ? -v[i] : v[i]);
-    mx = grupo_max<GL, ST>(mx);
+    mx = grupo_max<GL, ST>(mx, mask);
     if (mx >= LIM) reporta(E_ACUM, kid, idx0, mx, e);
     int sh = bitlen(mx) - 7;
     if (desloca(mx, sh) > 127) sh += 1;

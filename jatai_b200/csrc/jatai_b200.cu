@@ -31,6 +31,7 @@ static int g_tn = 0;                 // tile width of the tensor-core GEMM: 0 au
 
 static int fim() { return (int)cudaGetLastError(); }
 static unsigned nblocos16(long long n16) { return (unsigned)((n16 + 255) / 256); }
+static unsigned nblocos16u(long long n16, int U) { return (unsigned)((n16 + 256LL * U - 1) / (256LL * U)); }      // U chunks per thread
 
 typedef CUresult (*PFN_tmap)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                              const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -208,22 +209,22 @@ int jt_quant(const void* acc, const void* e, void* m, void* E, long long nblocos
 int jt_soma(const void* xm, const void* xE, const void* ym, const void* yE, void* zm, void* zE, long long nblocos, int kid) {
     const long long n16 = JT_N16;
 #define ARGS (const int8_t*)xm, (const int8_t*)xE, (const int8_t*)ym, (const int8_t*)yE, (int8_t*)zm, (int8_t*)zE, n16, kid
-    if (g_blk == 32) k_soma<32><<<nblocos16(n16), 256, 0, g_stream>>>(ARGS);
-    else k_soma<128><<<nblocos16(n16), 256, 0, g_stream>>>(ARGS);
+    if (g_blk == 32) k_soma<32><<<nblocos16u(n16, 4), 256, 0, g_stream>>>(ARGS);
+    else k_soma<128><<<nblocos16u(n16, 4), 256, 0, g_stream>>>(ARGS);
 #undef ARGS
     return fim();
 }
 int jt_relu2(const void* hm, const void* hE, void* am, void* aE, long long nblocos, int kid) {
     const long long n16 = JT_N16;
-    if (g_blk == 32) k_relu2<32><<<nblocos16(n16), 256, 0, g_stream>>>((const int8_t*)hm, (const int8_t*)hE, (int8_t*)am, (int8_t*)aE, n16, kid);
-    else k_relu2<128><<<nblocos16(n16), 256, 0, g_stream>>>((const int8_t*)hm, (const int8_t*)hE, (int8_t*)am, (int8_t*)aE, n16, kid);
+    if (g_blk == 32) k_relu2<32><<<nblocos16u(n16, 4), 256, 0, g_stream>>>((const int8_t*)hm, (const int8_t*)hE, (int8_t*)am, (int8_t*)aE, n16, kid);
+    else k_relu2<128><<<nblocos16u(n16, 4), 256, 0, g_stream>>>((const int8_t*)hm, (const int8_t*)hE, (int8_t*)am, (int8_t*)aE, n16, kid);
     return fim();
 }
 int jt_relu2_back(const void* gm, const void* gE, const void* hm, const void* hE, void* om, void* oE, long long nblocos, int kid) {
     const long long n16 = JT_N16;
 #define ARGS (const int8_t*)gm, (const int8_t*)gE, (const int8_t*)hm, (const int8_t*)hE, (int8_t*)om, (int8_t*)oE, n16, kid
-    if (g_blk == 32) k_relu2_back<32><<<nblocos16(n16), 256, 0, g_stream>>>(ARGS);
-    else k_relu2_back<128><<<nblocos16(n16), 256, 0, g_stream>>>(ARGS);
+    if (g_blk == 32) k_relu2_back<32><<<nblocos16u(n16, 4), 256, 0, g_stream>>>(ARGS);
+    else k_relu2_back<128><<<nblocos16u(n16, 4), 256, 0, g_stream>>>(ARGS);
 #undef ARGS
     return fim();
 }
