@@ -25,7 +25,17 @@ __global__ void __launch_bounds__(256) k_quant(const int* __restrict__ acc, cons
     int v[16], ee[16], q[16];
     le16_i32(acc + o, v);
     le16_i16(e + o, ee);
-    const int Eo = quant_geral<16, BLK / 16>(v, ee, q, kid, o);
+    // blocks whose elements all carry one exponent (attention outputs: one exponent per head) take the cheaper
+    // uniform quantiser; the choice is made per block, the lanes of a block always agree
+    int dif = 0;
+#pragma unroll
+    for (int i = 1; i < 16; i++) dif |= ee[i] ^ ee[0];
+    dif |= ee[0] ^ __shfl_sync(FULL, ee[0], (threadIdx.x & 31) & ~(BLK / 16 - 1));
+    dif = grupo_or<BLK / 16>(dif);
+    const unsigned m_uni = __ballot_sync(FULL, dif == 0);
+    int Eo;
+    if (dif == 0) Eo = quant_uniforme<16, BLK / 16>(v, ee[0], q, kid, o, m_uni);
+    else Eo = quant_geral<16, BLK / 16>(v, ee, q, kid, o, ~m_uni);
     if (ativo) grava16(m + o, q);
     if (lider) E[w] = (int8_t)Eo;
 }

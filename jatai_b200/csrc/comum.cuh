@@ -190,21 +190,21 @@ __device__ __forceinline__ int quant_uniforme(const int (&v)[NV], int e, int (&q
 
 // every value has its own exponent
 template <int NV, int GL, int ST = 1>
-__device__ __forceinline__ int quant_geral(const int (&v)[NV], const int (&e)[NV], int (&q)[NV], int kid, long long idx0) {
+__device__ __forceinline__ int quant_geral(const int (&v)[NV], const int (&e)[NV], int (&q)[NV], int kid, long long idx0, unsigned mask = FULL) {
     int topo = SEM_TOPO;
 #pragma unroll
     for (int i = 0; i < NV; i++) {
         if (v[i] >= LIM || v[i] <= -LIM) reporta(E_ACUM, kid, idx0 + i, v[i], e[i]);
         if (v[i] != 0) topo = max(topo, e[i] + bitlen(v[i]));
     }
-    topo = grupo_max<GL, ST>(topo);
+    topo = grupo_max<GL, ST>(topo, mask);
     int E = topo - 7, over = 0;
 #pragma unroll
     for (int i = 0; i < NV; i++) {
         q[i] = rnd(v[i], E - e[i], kid, idx0 + i);
         over |= (q[i] > 127) | (q[i] < -127);
     }
-    if (grupo_or<GL, ST>(over)) {
+    if (grupo_or<GL, ST>(over, mask)) {
         E += 1;
 #pragma unroll
         for (int i = 0; i < NV; i++) q[i] = rnd(v[i], E - e[i], kid, idx0 + i);
