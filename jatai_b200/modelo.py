@@ -57,6 +57,7 @@ class Modelo:
         # second stream for the weight-gradient GEMMs (single GPU, CUDA launcher only)
         usa_lado = hasattr(ops, "lib") and torch.device(dev).type == "cuda"
         self._lado = torch.cuda.Stream(device=dev) if usa_lado else None
+        self._pendente, self._feitos, self._k_lr_lado = None, set(), None
         na_gpu = redutor is not None and hasattr(ops, "lib") and torch.device(dev).type == "cuda"
         self._ramos = [torch.cuda.Stream(device=dev) for _ in range(3)] if na_gpu else []
 
@@ -88,13 +89,28 @@ class Modelo:
         with torch.cuda.stream(self._lado):
             ops.lib.jt_stream(self._lado.cuda_stream)
             try:
+                self._otimiza_pendente()
                 a, b = ops.transpoe(gy), ops.transpoe(x)
                 if self.redutor is None:
                     self._grads[nome] = ops.gemm(a, b, cru=True)
+                    self._pendente = nome
                 else:       # data parallel: only the transpositions and the row maxima now, the GEMM after the exchange
                     self._adiados.append((nome, a, b, ops.max_linha(a), ops.max_linha(b)))
             finally:
                 ops.lib.jt_stream(principal.cuda_stream)
+
+    def _otimiza_pendente(self):
+        """Single GPU, on the second stream: the optimiser step of the weight whose gradient was computed by the
+        previous call.  Safe because the second stream has just waited for the main stream, and by then the main
+        stream has queued its last read of that weight in this step (each weight is read once in the forward and
+        once, transposed, in the backward, right after its own `_grad_peso` call)."""
+        n = self._pendente
+        if n is None or self._k_lr_lado is None:
+            return
+        with self.reg.trecho("otimizador"), self.reg.trecho(n):
+            self._otimiza({n: self._grads[n]}, self._k_lr_lado)
+        self._feitos.add(n)
+        self._pendente = None
 
     def _gemms_adiados(self, maximos):
         """Data parallel, after the MAX collective: every weight-gradient GEMM with the global row maxima.  The GEMMs
@@ -132,10 +148,10 @@ class Modelo:
     # ------------------------------------------------------------------ the step
     def passo(self, tok, alvo, k_lr=None):
         """Forward (+ backward and update when k_lr is given).  Returns the loss as a tensor (report only, float)."""
-        perda = self.frente_tras(tok, alvo, treina=k_lr is not None)
+        perda = self.frente_tras(tok, alvo, treina=k_lr is not None, k_lr=k_lr)
         if k_lr is None:
             return perda
-        grads = self._grads
+        grads = {n: g for n, g in self._grads.items() if n not in self._feitos}       # the rest (all of them without a second stream)
         if self.redutor is not None:
             with self.reg.trecho("gradientes de peso"):
                 self._gemms_adiados(self.redutor.maximos_tudo([(ra, rb) for _, _, _, ra, rb in self._adiados]))
@@ -144,14 +160,17 @@ class Modelo:
             self._otimiza(grads, k_lr)
         return perda
 
-    def frente_tras(self, tok, alvo, treina=True):
+    def frente_tras(self, tok, alvo, treina=True, k_lr=None):
         """Forward and (if `treina`) backward.  Weight gradients land in self._grads (single GPU) or, data parallel,
-        their operands in self._adiados.  No communication happens here."""
+        their operands in self._adiados.  No communication happens here.  With `k_lr` on a single GPU the optimiser
+        step of each weight also runs here, on the second stream, as soon as its gradient exists."""
         ops, reg, p = self.ops, self.reg, self.p
         Bt, T = tok.shape
         tok = tok.reshape(-1).to(torch.int32).contiguous()
         alvo = alvo.reshape(-1).to(torch.int32).contiguous()
         self._grads, self._adiados = {}, []
+        self._pendente, self._feitos = None, set()
+        self._k_lr_lado = k_lr if (self.redutor is None and self._lado is not None) else None
         guardados = []
         with reg.trecho("forward"):
             with reg.trecho("embedding"):
@@ -209,6 +228,15 @@ class Modelo:
             with reg.trecho("embedding"):
                 self._grad_peso("emb", ops.um_quente(tok, self.V), gx)
         if self._lado is not None:
+            if self._pendente is not None and self._k_lr_lado is not None:
+                principal = torch.cuda.current_stream()
+                self._lado.wait_stream(principal)
+                with torch.cuda.stream(self._lado):
+                    ops.lib.jt_stream(self._lado.cuda_stream)
+                    try:
+                        self._otimiza_pendente()
+                    finally:
+                        ops.lib.jt_stream(principal.cuda_stream)
             torch.cuda.current_stream().wait_stream(self._lado)          # join the weight-gradient branch
         return perda
 
