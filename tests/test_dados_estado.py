@@ -1,0 +1,54 @@
+"""Data loader (the reference's recipe on a toy corpus) and bit-exact checkpoint / resume, on CPU with the oracle."""
+import json
+import os
+import tempfile
+
+import torch
+
+from oracle import spec
+
+
+def test_carregar_e_lote():
+    from jatai_b200 import dados
+    pasta = tempfile.mkdtemp()
+    for lingua in ("Portuguese", "English"):
+        with open(os.path.join(pasta, f"{lingua}.jsonl"), "w", encoding="utf-8") as fh:
+            for i in range(45):
+                fh.write(json.dumps({"text": f"{lingua} documento {i} ação"}) + "\n")
+    treino, val = dados.carregar(pasta)
+    assert treino.dtype == torch.long and int(treino.max()) < 256
+    doc0 = "Portuguese documento 0 ação".encode() + b"\n\n"
+    assert bytes(val[:len(doc0)].tolist()) == doc0                    # documents 0, 20, 40 of each language validate
+    assert len(val) == sum(len(f"{l} documento {i} ação".encode()) + 2 for l in ("Portuguese", "English") for i in (0, 20, 40))
+    g = torch.Generator().manual_seed(3)
+    x, y = dados.lote(treino, g, 4, 16)
+    assert x.shape == (4, 16) and torch.equal(x[:, 1:], y[:, :-1])
+
+
+def _modelo():
+    from jatai_b200 import modelo, ops, registro
+    ops.BLK = 32
+    reg = registro.Registro(tempfile.mkdtemp(), "ck", eco=False)
+    return modelo.Modelo(128, 64, 4, 128, 1, 0, "cpu", spec.Spec(32), reg)
+
+
+def _estado(m):
+    return [t.clone() for n in sorted(m.p) for par in (m.p[n], m.mom[n], m.res[n]) for t in par]
+
+
+def test_retomar_continua_bit_a_bit():
+    from jatai_b200 import dados, estado
+    fonte = dados.sintetico(5000, 9) % 128
+    a, ga = _modelo(), torch.Generator().manual_seed(1)
+    for _ in range(2):
+        a.passo(*dados.lote(fonte, ga, 2, 32), k_lr=4)
+    arq = os.path.join(tempfile.mkdtemp(), "ck.pt")
+    estado.salva(a, arq, 2, ga)
+    for _ in range(2):
+        a.passo(*dados.lote(fonte, ga, 2, 32), k_lr=4)
+    b, gb = _modelo(), torch.Generator().manual_seed(999)
+    assert estado.restaura(b, arq, gb) == 2
+    for _ in range(2):
+        b.passo(*dados.lote(fonte, gb, 2, 32), k_lr=4)
+    for i, (x, y) in enumerate(zip(_estado(a), _estado(b))):
+        assert torch.equal(x, y), f"state tensor {i} differs after resume"
