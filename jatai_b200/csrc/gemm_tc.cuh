@@ -155,6 +155,8 @@ __global__ void __launch_bounds__(Cfg<TNv>::N_THR, 1) k_gemm_tc(const __grid_con
         *aborta = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    if (tid < TM) RAs[tid] = -128;
+    if (tid < TNv) RBs[tid] = -128;
     if (wid == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(NTM * TNv) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -168,25 +170,31 @@ __global__ void __launch_bounds__(Cfg<TNv>::N_THR, 1) k_gemm_tc(const __grid_con
         // ------------------------------------------------------------------ TMA producer + column scale tables
         // lane l owns columns l, l+32, ... of the tile: their row maxima RB and, per chunk, their scales
         constexpr int NC = TNv / 32;
+        auto carrega = [&](int i) {
+            const int s = i % NST;
+            mbar_expect_tx(bar_full + 8 * s, STAGE_BYTES);
+            tma_2d(sbase + s * STAGE_BYTES, &mapA, (ped0 + i) * KC, m0, bar_full + 8 * s);
+            tma_2d(sbase + s * STAGE_BYTES + A_BYTES, &mapB, (ped0 + i) * KC, n0, bar_full + 8 * s);
+        };
+        // the first NST stages are free: their loads start before anything else, the row maxima (computed by the
+        // drain threads meanwhile) are only needed for the scale tables
+        if (lane == 0)
+            for (int i = 0; i < NST && i < pedacos_por_parte; i++) carrega(i);
+        __syncwarp();
+        asm volatile("bar.sync 2, %0;" ::"n"(N_EPI + 32) : "memory");
         int RBc[NC];
         const int8_t* ebc[NC];
 #pragma unroll
         for (int k = 0; k < NC; k++) {
             const int col = lane + 32 * k;
-            RBc[k] = RBg ? (int)RBg[n0 + col] : max_expoentes(EB + (size_t)(n0 + col) * nb, nb);
-            RBs[col] = RBc[k];
+            RBc[k] = RBs[col];
             ebc[k] = EB + (size_t)(n0 + col) * nb + (size_t)ped0 * NQ;
         }
         bool ok = true;
         for (int i = 0; i < pedacos_por_parte; i++) {
-            if (lane == 0 && ok) {
-                const int s = i % NST;
-                ok = espera(bar_empty + 8 * s, ((i / NST) & 1) ^ 1, aborta, kid, 1);
-                if (ok) {
-                    mbar_expect_tx(bar_full + 8 * s, STAGE_BYTES);
-                    tma_2d(sbase + s * STAGE_BYTES, &mapA, (ped0 + i) * KC, m0, bar_full + 8 * s);
-                    tma_2d(sbase + s * STAGE_BYTES + A_BYTES, &mapB, (ped0 + i) * KC, n0, bar_full + 8 * s);
-                }
+            if (lane == 0 && i >= NST) {
+                ok = espera(bar_empty + 8 * (i % NST), ((i / NST) & 1) ^ 1, aborta, kid, 1);
+                if (ok) carrega(i);
             }
             ok = __all_sync(FULL, ok);
             if (!ok) break;
@@ -243,8 +251,29 @@ __global__ void __launch_bounds__(Cfg<TNv>::N_THR, 1) k_gemm_tc(const __grid_con
         const int quarto = wid & 3;                               // tensor-memory lanes this warp may read
         const int cg = (wid - 2) >> 2;                            // column group of 32 within the tile
         const int lin = quarto * 32 + lane;                       // row of the tile = tensor-memory lane
-        const int RA = RAg ? (int)RAg[m0 + lin] : max_expoentes(EA + (size_t)(m0 + lin) * nb, nb);
-        if (cg == 0) RAs[lin] = RA;
+        // row maxima of the tile's 128 rows of A and TNv rows of B: all drain threads share the reads (16-byte pieces,
+        // one round trip to L2) and combine in shared memory
+        {
+            const bool pecas = (nb & 15) == 0;
+            const int ppl = pecas ? nb >> 4 : 1, npec = (TM + TNv) * ppl;
+            for (int idx = et; idx < npec; idx += N_EPI) {
+                const int l = idx / ppl, pc = idx - l * ppl;
+                const bool deA = l < TM;
+                const int8_t* Rg = deA ? RAg : RBg;
+                const int lg = deA ? m0 + l : n0 + l - TM;
+                int v;
+                if (Rg) {
+                    if (pc) continue;
+                    v = Rg[lg];
+                } else {
+                    const int8_t* pe = (deA ? EA : EB) + (size_t)lg * nb;
+                    v = pecas ? max_expoentes(pe + 16 * pc, 16) : max_expoentes(pe, nb);
+                }
+                atomicMax(deA ? &RAs[l] : &RBs[l - TM], v);
+            }
+        }
+        asm volatile("bar.sync 2, %0;" ::"n"(N_EPI + 32) : "memory");
+        const int RA = RAs[lin];
         const int8_t* ea_lin = EA + (size_t)(m0 + lin) * nb + (size_t)ped0 * NQ;
         auto le_exp = [&](int c) -> uint32_t {
             if (NQ == 4) return *reinterpret_cast<const uint32_t*>(ea_lin + 4 * c);
