@@ -55,45 +55,6 @@ __global__ void __launch_bounds__(256) k_quant(const int* __restrict__ acc, cons
     const long long nth_ = (long long)gridDim.x * blockDim.x;                             \
     const long long t0_ = (long long)blockIdx.x * blockDim.x + threadIdx.x;
 
-__device__ __forceinline__ void bytes_para_float(const uint4& r, float (&f)[16]) {
-    const uint32_t u[4] = {r.x, r.y, r.z, r.w};
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-        f[4 * i + 0] = (float)(int)(int8_t)(u[i] & 0xff);
-        f[4 * i + 1] = (float)(int)(int8_t)((u[i] >> 8) & 0xff);
-        f[4 * i + 2] = (float)(int)(int8_t)((u[i] >> 16) & 0xff);
-        f[4 * i + 3] = (float)((int)u[i] >> 24);
-    }
-}
-
-// Block quantiser in fp32 for integer-valued floats below 2^24 that share the exponent e (exact: ops.py:58-72).
-// The largest magnitude gives bitlen through its exponent field; one FFMA against 1.5*2^23 rounds v * 2^-sh half
-// to even (the low byte of the result's bit pattern is the mantissa); the "one more bit" retry is decided on the
-// maximum alone, because rounding is monotone.  Returns E; `pac` receives the 16 mantissas.
-template <int GL, int ST = 1>
-__device__ __forceinline__ int quant_f32(const float (&f)[16], int e, uint4& pac, int kid, long long idx0, unsigned mask = FULL) {
-    float mx = 0.f;
-#pragma unroll
-    for (int i = 0; i < 16; i++) mx = fmaxf(mx, fabsf(f[i]));
-#pragma unroll
-    for (int o = GL / 2; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(mask, mx, o * ST));
-    const int expo = (__float_as_int(mx) >> 23) - 127;               // floor(log2 mx) for mx >= 1
-    int sh = expo - 6;                                               // bitlen - 7
-    float sc = __int_as_float((127 - sh) << 23);                     // 2^-sh
-    if ((__float_as_int(fmaf(mx, sc, 12582912.0f)) & 0x1ff) > 127) { sh += 1; sc *= 0.5f; }
-    const int E = e + sh;
-    if (mx == 0.f || E < -126) { pac = make_uint4(0, 0, 0, 0); return E_ZERO; }
-    if (E > 126) reporta(E_EXP, kid, idx0, E, e);
-    uint32_t r[16];
-#pragma unroll
-    for (int i = 0; i < 16; i++) r[i] = (uint32_t)__float_as_int(fmaf(f[i], sc, 12582912.0f));
-    pac.x = __byte_perm(__byte_perm(r[0], r[1], 0x0040), __byte_perm(r[2], r[3], 0x0040), 0x5410);
-    pac.y = __byte_perm(__byte_perm(r[4], r[5], 0x0040), __byte_perm(r[6], r[7], 0x0040), 0x5410);
-    pac.z = __byte_perm(__byte_perm(r[8], r[9], 0x0040), __byte_perm(r[10], r[11], 0x0040), 0x5410);
-    pac.w = __byte_perm(__byte_perm(r[12], r[13], 0x0040), __byte_perm(r[14], r[15], 0x0040), 0x5410);
-    return E;
-}
-
 // z = x + y.  ops.py:128-132: ec = max(xE, yE) - 21; v = rnd(x, ec - xE) + rnd(y, ec - yE); quant(v, ec).
 // With hi / lo = the operand of larger / smaller exponent and d their distance, v = 2^(21-dl) * w where dl = min(d, 21),
 // w = hi * 2^dl + lo' and lo' = lo (d <= 21) or rnd(lo, d - 21) (the specification rounds the far operand first).
@@ -346,7 +307,8 @@ __global__ void __launch_bounds__(256) k_transpoe(const int8_t* __restrict__ X, 
     }
 }
 
-// Transposition for block 32, wide tiles: 128 rows x 256 columns per CTA.  A thread owns a 32-row block of 4
+// Transposition for block 32, wide tiles: TR (32, 64 or 128) rows x 256 columns per CTA of 2 TR threads; the launcher
+// takes the tallest tile that still gives every SM a CTA.  A thread owns a 32-row block of 4
 // adjacent columns (one 32-bit word per row) and quantises the 4 new blocks without leaving its registers.
 // The quantiser runs in fp32, exactly: a mantissa times 2^(e - eref) is exact in fp32, the largest magnitude gives
 // top = max(e + bitlen(v)) through its exponent field, and one FFMA against 1.5*2^23 rounds v * 2^(e - E) half to
@@ -368,9 +330,10 @@ __device__ __noinline__ void transpoe32_lento(const uint32_t (*tile)[T32_PW], co
     *Edst = (int8_t)Eo;
 }
 
-__global__ void __launch_bounds__(256, 2) k_transpoe32(const int8_t* __restrict__ X, const int8_t* __restrict__ EX, int8_t* __restrict__ Y,
-                                                       int8_t* __restrict__ EY, int R, int C, int kid) {
-    constexpr int TR = 128, TC = 256, PW = T32_PW;
+template <int TR>
+__global__ void __launch_bounds__(2 * TR, 256 / TR) k_transpoe32(const int8_t* __restrict__ X, const int8_t* __restrict__ EX, int8_t* __restrict__ Y,
+                                                                 int8_t* __restrict__ EY, int R, int C, int kid) {
+    constexpr int TC = 256, PW = T32_PW, NT = 2 * TR;
     __shared__ uint32_t tile[TR][PW];
     __shared__ __align__(4) int8_t et[TR][8];
     const int r0 = blockIdx.y * TR, c0 = blockIdx.x * TC;
@@ -378,7 +341,7 @@ __global__ void __launch_bounds__(256, 2) k_transpoe32(const int8_t* __restrict_
     const int nbx = C / 32, nby = R / 32;
 #pragma unroll
     for (int k = 0; k < 8; k++) {
-        const int idx = tid + 256 * k, lr = idx >> 4, c16 = idx & 15;
+        const int idx = tid + NT * k, lr = idx >> 4, c16 = idx & 15;
         const uint4 v = *reinterpret_cast<const uint4*>(X + (size_t)(r0 + lr) * C + c0 + c16 * 16);
         tile[lr][c16 * 4] = v.x; tile[lr][c16 * 4 + 1] = v.y; tile[lr][c16 * 4 + 2] = v.z; tile[lr][c16 * 4 + 3] = v.w;
     }

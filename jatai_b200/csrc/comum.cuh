@@ -223,4 +223,43 @@ __device__ __forceinline__ int quant_geral(const int (&v)[NV], const int (&e)[NV
     return E;
 }
 
+__device__ __forceinline__ void bytes_para_float(const uint4& r, float (&f)[16]) {
+    const uint32_t u[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        f[4 * i + 0] = (float)(int)(int8_t)(u[i] & 0xff);
+        f[4 * i + 1] = (float)(int)(int8_t)((u[i] >> 8) & 0xff);
+        f[4 * i + 2] = (float)(int)(int8_t)((u[i] >> 16) & 0xff);
+        f[4 * i + 3] = (float)((int)u[i] >> 24);
+    }
+}
+
+// Block quantiser in fp32 for integer-valued floats below 2^24 that share the exponent e (exact: ops.py:58-72).
+// The largest magnitude gives bitlen through its exponent field; one FFMA against 1.5*2^23 rounds v * 2^-sh half
+// to even (the low byte of the result's bit pattern is the mantissa); the "one more bit" retry is decided on the
+// maximum alone, because rounding is monotone.  Returns E; `pac` receives the 16 mantissas.
+template <int GL, int ST = 1>
+__device__ __forceinline__ int quant_f32(const float (&f)[16], int e, uint4& pac, int kid, long long idx0, unsigned mask = FULL) {
+    float mx = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; i++) mx = fmaxf(mx, fabsf(f[i]));
+#pragma unroll
+    for (int o = GL / 2; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(mask, mx, o * ST));
+    const int expo = (__float_as_int(mx) >> 23) - 127;               // floor(log2 mx) for mx >= 1
+    int sh = expo - 6;                                               // bitlen - 7
+    float sc = __int_as_float((127 - sh) << 23);                     // 2^-sh
+    if ((__float_as_int(fmaf(mx, sc, 12582912.0f)) & 0x1ff) > 127) { sh += 1; sc *= 0.5f; }
+    const int E = e + sh;
+    if (mx == 0.f || E < -126) { pac = make_uint4(0, 0, 0, 0); return E_ZERO; }
+    if (E > 126) reporta(E_EXP, kid, idx0, E, e);
+    uint32_t r[16];
+#pragma unroll
+    for (int i = 0; i < 16; i++) r[i] = (uint32_t)__float_as_int(fmaf(f[i], sc, 12582912.0f));
+    pac.x = __byte_perm(__byte_perm(r[0], r[1], 0x0040), __byte_perm(r[2], r[3], 0x0040), 0x5410);
+    pac.y = __byte_perm(__byte_perm(r[4], r[5], 0x0040), __byte_perm(r[6], r[7], 0x0040), 0x5410);
+    pac.z = __byte_perm(__byte_perm(r[8], r[9], 0x0040), __byte_perm(r[10], r[11], 0x0040), 0x5410);
+    pac.w = __byte_perm(__byte_perm(r[12], r[13], 0x0040), __byte_perm(r[14], r[15], 0x0040), 0x5410);
+    return E;
+}
+
 }  // namespace jt

@@ -25,9 +25,15 @@ struct SaidaGemm {
 // group of RPW rows (4 rows of a 128-column tile, 8 of a 64-column one), so the 8 lanes of a shared-memory phase
 // read different rows (no bank conflict) while the lanes that share a row still write contiguous bytes; the
 // lanes of one exponent block sit RPW apart.
+//
+// Fast path of the block outputs (taken by a whole warp or not at all): when every accumulator of the warp's rows is
+// below 2^24 and the column exponents of each block spread over at most 64, the values acc * 2^(RB_j - min RB) are exact
+// in fp32 and the fp32 quantiser gives the bits of the integer one.  It needs, from the caller, RBf[j] = 2^(RB_j - min
+// of j's block) and RBm[b] = that minimum, RBm[4 + b] = the block's maximum; RBf == nullptr disables it.
 template <int BLK, int MODO, int NTH, int TNv = TN>
 __device__ __forceinline__ void epilogo_tile(const int* acc_s, const int* RAs, const int* RBs, int linhas, int m0, int n0, int N,
-                                             const SaidaGemm& S, bool atomico, bool grava_e, int kid, int tid) {
+                                             const SaidaGemm& S, bool atomico, bool grava_e, int kid, int tid,
+                                             const float* RBf = nullptr, const int* RBm = nullptr) {
     constexpr int GL = BLK / 16;
     constexpr int RPW = 512 / TNv;             // rows a warp handles per iteration: 32 lanes / (TNv / 16) chunks per row
     constexpr int PITCHv = TNv + 4;
@@ -64,12 +70,60 @@ __device__ __forceinline__ void epilogo_tile(const int* acc_s, const int* RAs, c
             }
             continue;
         }
-        int e[16], q[16];
-#pragma unroll
-        for (int k = 0; k < 16; k++) e[k] = ra + RBs[ch * 16 + k];
-        const int E = quant_geral<16, GL, RPW>(v, e, q, kid, o);
         const bool lider = (ch % GL) == 0;
         const long long oe = (long long)gi * (N / BLK) + gj / BLK;
+        int q[16], E;
+        bool rapido = false;
+        if (RBf) {
+            int amax = 0;
+#pragma unroll
+            for (int k = 0; k < 16; k++) amax = max(amax, abs(v[k]));
+            const int b = ch * 16 / BLK;
+            rapido = __all_sync(FULL, amax < (1 << 24) && RBm[4 + b] - RBm[b] <= 64);
+            if (rapido) {
+                float f[16];
+#pragma unroll
+                for (int k = 0; k < 4; k++) {
+                    const float4 sc = *reinterpret_cast<const float4*>(RBf + ch * 16 + 4 * k);
+                    f[4 * k] = (float)v[4 * k] * sc.x; f[4 * k + 1] = (float)v[4 * k + 1] * sc.y;
+                    f[4 * k + 2] = (float)v[4 * k + 2] * sc.z; f[4 * k + 3] = (float)v[4 * k + 3] * sc.w;
+                }
+                uint4 pac;
+                E = quant_f32<GL, RPW>(f, ra + RBm[b], pac, kid, o);
+                if (MODO == 0 || MODO == 3) {
+                    *reinterpret_cast<uint4*>(S.Cm + o) = pac;
+                    if (lider) S.CE[oe] = (int8_t)E;
+                }
+                if (MODO == 0) continue;
+                if (MODO == 3) {                   // relu2 of the quantised h (ops.py:134-137): squares <= 16129 are exact in fp32
+                    bytes_para_float(pac, f);
+#pragma unroll
+                    for (int k = 0; k < 16; k++) { const float rr = fmaxf(f[k], 0.f); f[k] = rr * rr; }
+                    const int E2 = quant_f32<GL, RPW>(f, 2 * E, pac, kid, o);
+                    *reinterpret_cast<uint4*>(S.Om2 + o) = pac;
+                    if (lider) S.OE2[oe] = (int8_t)E2;
+                    continue;
+                }
+                if (MODO == 4) {                   // relu2_back (ops.py:139-141): |g h 2| <= 32258
+                    float h[16];
+                    bytes_para_float(pac, f);
+                    bytes_para_float(*reinterpret_cast<const uint4*>(S.Xm + o), h);
+#pragma unroll
+                    for (int k = 0; k < 16; k++) f[k] = f[k] * fmaxf(h[k], 0.f) * 2.f;
+                    const int E2 = quant_f32<GL, RPW>(f, E + (int)S.XE[oe], pac, kid, o);
+                    *reinterpret_cast<uint4*>(S.Cm + o) = pac;
+                    if (lider) S.CE[oe] = (int8_t)E2;
+                    continue;
+                }
+                desempacota16(pac, q);             // MODO 2 goes on in integers: its sums reach 2^28
+            }
+        }
+        if (!rapido) {
+            int e[16];
+#pragma unroll
+            for (int k = 0; k < 16; k++) e[k] = ra + RBs[ch * 16 + k];
+            E = quant_geral<16, GL, RPW>(v, e, q, kid, o);
+        }
         if (MODO == 0) {
             grava16(S.Cm + o, q);
             if (lider) S.CE[oe] = (int8_t)E;

@@ -10,7 +10,7 @@
 // instruction starts a fresh accumulator (tensor-memory stage) that is drained, aligned and added in registers;
 // with BLK = 128 four instructions accumulate in tensor memory before one drain.
 //
-// CTA = one 128 x 128 tile of C (optionally one K range of it: split-K for raw outputs), 18 warps:
+// CTA = one 128 x TNv tile of C (optionally one K range of it: split-K for raw outputs), 2 + TNv / 8 warps (TNv = 128 below):
 //   warp 0       TMA producer (one lane): A and B tiles of 128 rows x 128 bytes of K, SWIZZLE_128B, NST-stage ring;
 //                all 32 lanes also build, ahead of the drain, the table of column scales 2^-(RB_j - eb_jb) it reads
 //   warp 1       allocates tensor memory, issues the MMAs (one thread), frees tensor memory
@@ -34,13 +34,21 @@ struct Cfg {
     static constexpr int N_DW = TNv / 8;                       // drain warps: 4 lane quarters x (TNv / 32) column groups
     static constexpr int N_EPI = N_DW * 32, N_THR = 64 + N_EPI, PITCHv = TNv + 4;
     static constexpr uint32_t B_BYTES = TNv * KC, STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr uint32_t OFF_ACC = NST * STAGE_BYTES;
-    static constexpr uint32_t OFF_TAB = OFF_ACC + TM * PITCHv * 4;          // scale table ring: [NTB][4][TNv] floats
+    // the staged accumulators of the output stage reuse the operand ring: when a drain thread stores its accumulators
+    // it has seen the commit of the last MMA, so every TMA load has landed and every operand read has finished
+    static constexpr uint32_t OFF_ACC = 0;
+    static_assert(TM * PITCHv * 4 <= NST * STAGE_BYTES, "staged accumulators must fit in the operand ring");
+    static constexpr uint32_t OFF_TAB = NST * STAGE_BYTES;                  // scale table ring: [NTB][4][TNv] floats
     static constexpr uint32_t OFF_RA = OFF_TAB + NTB * 4 * TNv * 4;
     static constexpr uint32_t OFF_RB = OFF_RA + TM * 4;
-    static constexpr uint32_t OFF_BAR = OFF_RB + TNv * 4;
+    static constexpr uint32_t OFF_RBF = OFF_RB + TNv * 4;                   // 2^(RB_j - minimum of j's block), floats
+    static constexpr uint32_t OFF_RBM = OFF_RBF + TNv * 4;                  // minimum and maximum RB of each block: int[4] + int[4]
+    static constexpr uint32_t OFF_BAR = OFF_RBM + 32;
     static constexpr uint32_t OFF_MISC = OFF_BAR + (2 * NST + 2 * NTM + 2 * NTB) * 8;
     static constexpr uint32_t SMEM_BYTES = OFF_MISC + 16 + 1024;            // + slack to align the base to 1024 bytes
+    // 64-column tiles: two CTAs per SM (2 x 256 columns of tensor memory, 2 x ~100 KB of shared memory, <= 102 registers):
+    // the prologue and the output stage of one overlap the main loop of the other
+    static constexpr int CTAS_SM = TNv == 64 ? 2 : 1;
     // instruction descriptor kind::i8: D = s32, A = B = s8, both K-major, N = TNv, M = 128
     static constexpr uint32_t IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TNv >> 3) << 17) | ((uint32_t)(TM >> 4) << 24);
 };
@@ -120,14 +128,14 @@ __device__ __forceinline__ float pot2(int e) { return __int_as_float((127 + e) <
 // VIA 0: round with one FFMA against 1.5*2^23 and add the bit pattern (valid while |p * 2^(4-s)| < 2^22);
 // VIA 1: exact float product, cvt.rni to int (valid for every input).
 template <int BLK, int MODO, int VIA, int TNv>
-__global__ void __launch_bounds__(Cfg<TNv>::N_THR, 1) k_gemm_tc(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
+__global__ void __launch_bounds__(Cfg<TNv>::N_THR, Cfg<TNv>::CTAS_SM) k_gemm_tc(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                                                       const int8_t* __restrict__ EA, const int8_t* __restrict__ EB,
                                                       const int8_t* __restrict__ RAg, const int8_t* __restrict__ RBg, SaidaGemm S, int M, int N,
                                                       int K, int pedacos_por_parte, int kid) {
     constexpr int NQ = KC / BLK;                 // K-blocks per 128-byte chunk: 4 (BLK 32) or 1 (BLK 128)
     using C_ = Cfg<TNv>;
     constexpr int N_DW = C_::N_DW, N_EPI = C_::N_EPI, PITCHv = C_::PITCHv;
-    constexpr uint32_t STAGE_BYTES = C_::STAGE_BYTES, OFF_ACC = C_::OFF_ACC, OFF_TAB = C_::OFF_TAB, OFF_RA = C_::OFF_RA, OFF_RB = C_::OFF_RB,
+    constexpr uint32_t STAGE_BYTES = C_::STAGE_BYTES, OFF_ACC = C_::OFF_ACC, OFF_TAB = C_::OFF_TAB, OFF_RA = C_::OFF_RA, OFF_RB = C_::OFF_RB, OFF_RBF = C_::OFF_RBF, OFF_RBM = C_::OFF_RBM,
                        OFF_BAR = C_::OFF_BAR, OFF_MISC = C_::OFF_MISC, IDESC = C_::IDESC;
     static_assert(TNv == 128 || (TNv == 64 && BLK == 32), "64-column tiles exist for block 32 only");
     extern __shared__ unsigned char smem_bruto[];
@@ -137,6 +145,8 @@ __global__ void __launch_bounds__(Cfg<TNv>::N_THR, 1) k_gemm_tc(const __grid_con
     float* tabB = reinterpret_cast<float*>(smem + OFF_TAB);          // [NTB][4][TN]
     int* RAs = reinterpret_cast<int*>(smem + OFF_RA);
     int* RBs = reinterpret_cast<int*>(smem + OFF_RB);
+    float* RBf = reinterpret_cast<float*>(smem + OFF_RBF);
+    int* RBm = reinterpret_cast<int*>(smem + OFF_RBM);
     const uint32_t bar_full = sbase + OFF_BAR, bar_empty = bar_full + NST * 8, bar_tfull = bar_empty + NST * 8, bar_tempty = bar_tfull + NTM * 8;
     const uint32_t bar_bfull = bar_tempty + NTM * 8, bar_bempty = bar_bfull + NTB * 8;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + OFF_MISC);
@@ -157,6 +167,7 @@ __global__ void __launch_bounds__(Cfg<TNv>::N_THR, 1) k_gemm_tc(const __grid_con
     }
     if (tid < TM) RAs[tid] = -128;
     if (tid < TNv) RBs[tid] = -128;
+    if (tid < 8) RBm[tid] = tid < 4 ? 1000 : -1000;
     if (wid == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(NTM * TNv) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -180,16 +191,21 @@ __global__ void __launch_bounds__(Cfg<TNv>::N_THR, 1) k_gemm_tc(const __grid_con
         // drain threads meanwhile) are only needed for the scale tables
         if (lane == 0)
             for (int i = 0; i < NST && i < pedacos_por_parte; i++) carrega(i);
+        const int8_t* ebc[NC];
+        uint32_t w[NC];                           // block exponents of this lane's columns for the next chunk, read one chunk ahead
+        auto le_w = [&](int i) {
+#pragma unroll
+            for (int k = 0; k < NC; k++)
+                w[k] = NQ == 4 ? *reinterpret_cast<const uint32_t*>(ebc[k] + 4 * i) : (uint32_t)(uint8_t)ebc[k][i];
+        };
+#pragma unroll
+        for (int k = 0; k < NC; k++) ebc[k] = EB + (size_t)(n0 + lane + 32 * k) * nb + (size_t)ped0 * NQ;
+        le_w(0);
         __syncwarp();
         asm volatile("bar.sync 2, %0;" ::"n"(N_EPI + 32) : "memory");
         int RBc[NC];
-        const int8_t* ebc[NC];
 #pragma unroll
-        for (int k = 0; k < NC; k++) {
-            const int col = lane + 32 * k;
-            RBc[k] = RBs[col];
-            ebc[k] = EB + (size_t)(n0 + col) * nb + (size_t)ped0 * NQ;
-        }
+        for (int k = 0; k < NC; k++) RBc[k] = RBs[lane + 32 * k];
         bool ok = true;
         for (int i = 0; i < pedacos_por_parte; i++) {
             if (lane == 0 && i >= NST) {
@@ -199,10 +215,6 @@ __global__ void __launch_bounds__(Cfg<TNv>::N_THR, 1) k_gemm_tc(const __grid_con
             ok = __all_sync(FULL, ok);
             if (!ok) break;
             const int sl = i % NTB;
-            uint32_t w[NC];
-#pragma unroll
-            for (int k = 0; k < NC; k++)
-                w[k] = NQ == 4 ? *reinterpret_cast<const uint32_t*>(ebc[k] + 4 * i) : (uint32_t)(uint8_t)ebc[k][i];
             ok = __all_sync(FULL, espera(bar_bempty + 8 * sl, ((i / NTB) & 1) ^ 1, aborta, kid, 5));
             if (!ok) break;
 #pragma unroll
@@ -213,6 +225,7 @@ __global__ void __launch_bounds__(Cfg<TNv>::N_THR, 1) k_gemm_tc(const __grid_con
                     tabB[(sl * 4 + q) * TNv + lane + 32 * k] = pot2(-sb);
                 }
             mbar_arrive(bar_bfull + 8 * sl);
+            if (i + 1 < pedacos_por_parte) le_w(i + 1);
         }
     } else if (wid == 1) {
         // ------------------------------------------------------------------ MMA issuer
@@ -251,6 +264,12 @@ __global__ void __launch_bounds__(Cfg<TNv>::N_THR, 1) k_gemm_tc(const __grid_con
         const int quarto = wid & 3;                               // tensor-memory lanes this warp may read
         const int cg = (wid - 2) >> 2;                            // column group of 32 within the tile
         const int lin = quarto * 32 + lane;                       // row of the tile = tensor-memory lane
+        const int8_t* ea_lin = EA + (size_t)(m0 + lin) * nb + (size_t)ped0 * NQ;
+        auto le_exp = [&](int c) -> uint32_t {
+            if (NQ == 4) return *reinterpret_cast<const uint32_t*>(ea_lin + 4 * c);
+            return (uint32_t)(uint8_t)ea_lin[c];
+        };
+        uint32_t eaw = le_exp(0), eaw_prox = 0;
         // row maxima of the tile's 128 rows of A and TNv rows of B: all drain threads share the reads (16-byte pieces,
         // one round trip to L2) and combine in shared memory
         {
@@ -274,12 +293,19 @@ __global__ void __launch_bounds__(Cfg<TNv>::N_THR, 1) k_gemm_tc(const __grid_con
         }
         asm volatile("bar.sync 2, %0;" ::"n"(N_EPI + 32) : "memory");
         const int RA = RAs[lin];
-        const int8_t* ea_lin = EA + (size_t)(m0 + lin) * nb + (size_t)ped0 * NQ;
-        auto le_exp = [&](int c) -> uint32_t {
-            if (NQ == 4) return *reinterpret_cast<const uint32_t*>(ea_lin + 4 * c);
-            return (uint32_t)(uint8_t)ea_lin[c];
-        };
-        uint32_t eaw = le_exp(0), eaw_prox = 0;
+        if (MODO != 1 && et < TNv) {
+            // what the fp32 path of the output stage needs: each block's extreme column exponents and the column scales
+            const int rb = RBs[et], b = et / BLK;
+            int mn = rb, mx = rb;
+#pragma unroll
+            for (int o = 16; o; o >>= 1) { mn = min(mn, __shfl_xor_sync(FULL, mn, o)); mx = max(mx, __shfl_xor_sync(FULL, mx, o)); }
+            if (BLK > 32) {
+                if (lane == 0) { atomicMin(&RBm[b], mn); atomicMax(&RBm[4 + b], mx); }
+                asm volatile("bar.sync 3, %0;" ::"n"(TNv) : "memory");
+                mn = RBm[b];
+            } else if (lane == 0) { RBm[b] = mn; RBm[4 + b] = mx; }
+            RBf[et] = pot2(min(rb - mn, 100));
+        }
         int acc[32];
 #pragma unroll
         for (int j = 0; j < 32; j++) acc[j] = 0;
@@ -290,10 +316,12 @@ __global__ void __launch_bounds__(Cfg<TNv>::N_THR, 1) k_gemm_tc(const __grid_con
             if (c + 1 < pedacos_por_parte) eaw_prox = le_exp(c + 1);
             ok = __all_sync(FULL, espera(bar_bfull + 8 * sl, (c / NTB) & 1, aborta, kid, 6));
             if (!ok) break;
-#pragma unroll 1
+            // one tensor-memory stage per K-block of the chunk when both count 4: stage and phase are compile-time per q
+            constexpr bool FIXO = NQ == NTM;
+#pragma unroll
             for (int q = 0; q < NQ; q++, f++) {
-                const int t = f % NTM;
-                ok = __all_sync(FULL, espera(bar_tfull + 8 * t, (f / NTM) & 1, aborta, kid, 4));
+                const int t = FIXO ? q : f % NTM;
+                ok = __all_sync(FULL, espera(bar_tfull + 8 * t, (FIXO ? c : f / NTM) & 1, aborta, kid, 4));
                 if (!ok) break;
                 tc_fence_depois();
                 uint32_t d[32];
@@ -332,7 +360,7 @@ __global__ void __launch_bounds__(Cfg<TNv>::N_THR, 1) k_gemm_tc(const __grid_con
             *reinterpret_cast<int4*>(acc_s + lin * PITCHv + cg * 32 + j) = make_int4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
         // the only barrier of the drain warps: reached by every drain thread exactly once, aborted or not
         asm volatile("bar.sync 1, %0;" ::"n"(N_EPI) : "memory");
-        epilogo_tile<BLK, MODO, N_EPI, TNv>(acc_s, RAs, RBs, TM, m0, n0, N, S, gridDim.z > 1, blockIdx.z == 0, kid, et);
+        epilogo_tile<BLK, MODO, N_EPI, TNv>(acc_s, RAs, RBs, TM, m0, n0, N, S, gridDim.z > 1, blockIdx.z == 0, kid, et, RBf, RBm);
     }
     tc_fence_antes();
     __syncthreads();

@@ -70,6 +70,8 @@ static int lanca_tc(const CUtensorMap& mA, const CUtensorMap& mB, const int8_t* 
     if (!pronto) {
         cudaError_t c = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C_::SMEM_BYTES);
         if (c != cudaSuccess) return (int)c;
+        c = cudaFuncSetAttribute(k, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
+        if (c != cudaSuccess) return (int)c;
         pronto = true;
     }
     const dim3 grade(N / TNv, M / tc::TM, partes);
@@ -91,11 +93,10 @@ static int gemm_blk(const int8_t* A, const int8_t* EA, const int8_t* B, const in
     if (M <= 0 || N <= 0 || K <= 0 || M % 64 || N % TN || K % BLK || K % 32 || modo < 0 || modo > 4) return (int)cudaErrorInvalidValue;
     const bool alinhado = (((uintptr_t)A | (uintptr_t)B) & 15) == 0 && (((uintptr_t)EA | (uintptr_t)EB) & 3) == 0;
     bool usa_tc = g_via != 2 && M % tc::TM == 0 && K % tc::KC == 0 && alinhado;
-    // 64-column tiles (block 32 only) when they finish sooner: a 64-column tile costs ~0.7 of a 128-column one (measured 0.6-0.75), and
-    // the GEMM takes ceil(tiles / 148) rounds of one CTA per SM
+    // 64-column tiles (block 32 only) when 128-column tiles would leave at least half of the 148 SMs without a CTA: alone on
+    // an SM a 64-column tile takes ~0.77 of a 128-column one, but two of them sharing an SM take ~1.13 (measured)
     const long long tiles128 = (long long)(N / TN) * (M / tc::TM);
-    const double custo128 = (double)((tiles128 + 147) / 148), custo64 = 0.7 * (double)((2 * tiles128 + 147) / 148);
-    const bool estreito = BLK == 32 && usa_tc && g_tn != 128 && (g_tn == 64 || custo64 < custo128 - 0.01);
+    const bool estreito = BLK == 32 && usa_tc && g_tn != 128 && (g_tn == 64 || 2 * tiles128 <= 148);
     const int tn = estreito ? 64 : TN;
     CUtensorMap mA, mB;
     if (usa_tc) usa_tc = faz_mapa(&mA, A, M, K) && faz_mapa(&mB, B, N, K, tn);
@@ -245,7 +246,12 @@ int jt_peso(void* Wm, void* WE, const void* Mm, const void* ME, void* Rm, void* 
 int jt_transpoe(const void* X, const void* EX, void* Y, void* EY, int R, int C, int kid) {
     if (R <= 0 || C <= 0 || R % 128 || C % 64 || C % g_blk) return (int)cudaErrorInvalidValue;
     if (g_blk == 32 && C % 256 == 0 && ((uintptr_t)EX & 3) == 0) {
-        k_transpoe32<<<dim3(C / 256, R / 128), 256, 0, g_stream>>>((const int8_t*)X, (const int8_t*)EX, (int8_t*)Y, (int8_t*)EY, R, C, kid);
+        const long long t128 = (long long)(C / 256) * (R / 128);
+#define ARGS (const int8_t*)X, (const int8_t*)EX, (int8_t*)Y, (int8_t*)EY, R, C, kid
+        if (t128 >= 148) k_transpoe32<128><<<dim3(C / 256, R / 128), 256, 0, g_stream>>>(ARGS);
+        else if (2 * t128 >= 148) k_transpoe32<64><<<dim3(C / 256, R / 64), 128, 0, g_stream>>>(ARGS);
+        else k_transpoe32<32><<<dim3(C / 256, R / 32), 64, 0, g_stream>>>(ARGS);
+#undef ARGS
         return fim();
     }
     const dim3 grade(C / 64, R / 128);
