@@ -93,10 +93,12 @@ static int gemm_blk(const int8_t* A, const int8_t* EA, const int8_t* B, const in
     if (M <= 0 || N <= 0 || K <= 0 || M % 64 || N % TN || K % BLK || K % 32 || modo < 0 || modo > 4) return (int)cudaErrorInvalidValue;
     const bool alinhado = (((uintptr_t)A | (uintptr_t)B) & 15) == 0 && (((uintptr_t)EA | (uintptr_t)EB) & 3) == 0;
     bool usa_tc = g_via != 2 && M % tc::TM == 0 && K % tc::KC == 0 && alinhado;
-    // 64-column tiles (block 32 only) when 128-column tiles would leave at least half of the 148 SMs without a CTA: alone on
-    // an SM a 64-column tile takes ~0.77 of a 128-column one, but two of them sharing an SM take ~1.13 (measured)
+    // 64-column tiles (block 32 only), two CTAs per SM.  Alone on an SM such a tile takes ~0.77 of a 128-column one, so they
+    // win when 128-column tiles would leave half of the 148 SMs without a CTA; beyond that the pairs run without wave
+    // boundaries (~1.03 t/148 + 0.3 rounds of a 128-column tile, measured) against ceil(t/148) whole rounds
     const long long tiles128 = (long long)(N / TN) * (M / tc::TM);
-    const bool estreito = BLK == 32 && usa_tc && g_tn != 128 && (g_tn == 64 || 2 * tiles128 <= 148);
+    const double r128 = (double)((tiles128 + 147) / 148), r64 = 1.03 * (double)tiles128 / 148.0 + 0.3;
+    const bool estreito = BLK == 32 && usa_tc && g_tn != 128 && (g_tn == 64 || 2 * tiles128 <= 148 || r64 < r128);
     const int tn = estreito ? 64 : TN;
     CUtensorMap mA, mB;
     if (usa_tc) usa_tc = faz_mapa(&mA, A, M, K) && faz_mapa(&mB, B, N, K, tn);
