@@ -165,7 +165,9 @@ __global__ void __launch_bounds__(256) k_atencao(const int8_t* __restrict__ qm, 
     uint8_t* pT = reinterpret_cast<uint8_t*>(q_s + TI * PK);
     __shared__ int red[8];
     const int tid = threadIdx.x, ty = tid >> 5, lane = tid & 31;
-    const int bh = blockIdx.y, b = bh / H, h = bh % H, i0 = blockIdx.x * TI;
+    // causal work grows with the row tile: CTAs are dispatched in linear order, so the heaviest tiles of all heads go first
+    const int ordem = blockIdx.y * gridDim.x + blockIdx.x;
+    const int bh = ordem % gridDim.y, b = bh / H, h = bh % H, i0 = (gridDim.x - 1 - ordem / gridDim.y) * TI;
     const int ld = 3 * D, ldb = ld / blk, linha0 = b * T;
     const int emq = max_cabeca<HD>(qE, ldb, blk, linha0, T, h * HD, red, tid);
     const int emk = max_cabeca<HD>(qE, ldb, blk, linha0, T, D + h * HD, red, tid);
@@ -301,7 +303,8 @@ __global__ void __launch_bounds__(256) k_ab_linhas(ArgsTras A) {
     __shared__ int red[8];
     __shared__ int sl_s[TI];
     const int tid = threadIdx.x, ty = tid >> 5, lane = tid & 31;
-    const int bh = blockIdx.y, b = bh / H, h = bh % H, i0 = blockIdx.x * TI, linha0 = b * T;
+    const int ordem = blockIdx.y * gridDim.x + blockIdx.x;          // heaviest (last) row tiles of all heads first
+    const int bh = ordem % gridDim.y, b = bh / H, h = bh % H, i0 = (gridDim.x - 1 - ordem / gridDim.y) * TI, linha0 = b * T;
     int* est = A.est + bh * N_EST;
     const int emg = max_cabeca<HD>(A.goE, D / blk, blk, linha0, T, h * HD, red, tid);
     const int emv = max_cabeca<HD>(A.qE, 3 * D / blk, blk, linha0, T, 2 * D + h * HD, red, tid);
@@ -410,7 +413,8 @@ __global__ void __launch_bounds__(256) k_ab_colunas(ArgsTras A) {
     int* p_c = ds_c + TI * CP;        // [32][132] P of the chunk
     __shared__ int red[8];
     const int tid = threadIdx.x, ty = tid >> 5, lane = tid & 31;
-    const int bh = blockIdx.y, b = bh / H, h = bh % H, j0 = blockIdx.x * TI, linha0 = b * T;
+    const int ordem = blockIdx.y * gridDim.x + blockIdx.x;          // heaviest (first) key tiles of all heads first
+    const int bh = ordem % gridDim.y, b = bh / H, h = bh % H, j0 = (ordem / gridDim.y) * TI, linha0 = b * T;
     const int* est = A.est + bh * N_EST;
     const int emg = max_cabeca<HD>(A.goE, D / blk, blk, linha0, T, h * HD, red, tid);
     const int emq = max_cabeca<HD>(A.qE, 3 * D / blk, blk, linha0, T, h * HD, red, tid);

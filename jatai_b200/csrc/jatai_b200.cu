@@ -70,7 +70,9 @@ static int lanca_tc(const CUtensorMap& mA, const CUtensorMap& mB, const int8_t* 
     if (!pronto) {
         cudaError_t c = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C_::SMEM_BYTES);
         if (c != cudaSuccess) return (int)c;
-        c = cudaFuncSetAttribute(k, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
+        // shared memory for the resident CTAs and no more: what is left of the 256 KB serves the L1 (register spills)
+        c = cudaFuncSetAttribute(k, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                 (int)((C_::SMEM_BYTES + 1024) * C_::CTAS_SM * 100 / (228 * 1024)) + 1);
         if (c != cudaSuccess) return (int)c;
         pronto = true;
     }
