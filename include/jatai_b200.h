@@ -13,7 +13,8 @@
  *   - all launches go to the stream given to jt_stream (NULL = legacy default stream); nothing synchronises
  *     except jt_erro_le and jt_sincroniza, so a whole step can be captured in a CUDA graph;
  *   - every input and output is owned by the caller; the only device memory the library allocates is the
- *     workspace of jt_atencao_back (Bt*H*(8+T) ints, cudaMalloc on first use, reused afterwards);
+ *     workspace of jt_atencao_back (Bt*H*(8+T+T*T) ints - the T*T part, which carries intermediate matrices between
+ *     its kernels, only while it stays below 1 GiB - cudaMalloc on first use, reused and grown afterwards);
  *   - kernels never trap: a broken invariant is recorded in the device error record and the kernel goes on.
  *
  * Tensor formats (jatai_cuda.cu:3-9):
@@ -106,7 +107,8 @@ int jt_max_linha(const void* E, void* R8, int linhas, int nb, int kid);
 /* jt_atencao_back for callers that may not allocate device memory (fixed memory budgets, code running where
  * cudaMalloc is forbidden): same arguments and results, but the workspace lives in a fixed 4 MiB device array
  * inside the library instead of a cudaMalloc'd buffer, and no allocating routine is called.  Refuses
- * Bt*H*(8+T) > 2^20 with cudaErrorInvalidValue.  The first call on a device resolves the array's address: make it
+ * Bt*H*(8+T) > 2^20 with cudaErrorInvalidValue; when Bt*H*(8+T+T*T) does not fit either, its kernels recompute the
+ * intermediate matrices instead of handing them on (same bits, slower).  The first call on a device resolves the array's address: make it
  * outside stream capture.  All calls share the array; calls that overlap on the GPU race.
  * It has no counterpart in the reference. */
 int jt_atencao_back_fixo(const void* gom, const void* goE, const void* qm, const void* qE, const void* P, void* Gacc, void* Ge,

@@ -18,7 +18,10 @@
 //   k_ab1  max |gP| over j <= i                         (skipped by the upper-bound variant, which runs k_lim)
 //   k_ab2  gP' = rnd(gP, sh); s_lin; max |dS| (and the maxima the upper-bound variant needs)
 //   k_ab3q dS' = rnd(P (gP' - s_lin), sh2); gq = dS' . k          (row tiles)
-//   k_ab3k the same dS' recomputed per key tile; gk = dS'^T . q, gv = P^T . dO   (no atomics on the outputs)
+//   k_ab3k dS' per key tile; gk = dS'^T . q, gv = P^T . dO   (no atomics on the outputs)
+// When the workspace has room for a T x T int32 matrix per (sequence, head) (it stays in L2 at training sizes), gP is
+// computed once and handed on: k_ab1 stores gP, k_ab2 turns it into gP', k_ab3q into dS', k_ab3k reads dS'.  Without
+// it every phase recomputes dO . v^T from the operands.
 #pragma once
 #include "comum.cuh"
 
@@ -253,6 +256,7 @@ __global__ void __launch_bounds__(256) k_atencao(const int8_t* __restrict__ qm, 
 struct ArgsTras {
     const int8_t* gom; const int8_t* goE; const int8_t* qm; const int8_t* qE; const uint8_t* P;
     int* Gacc; int16_t* Ge; int* est; int* sl;           // est: [Bt*H][N_EST]; sl: [Bt*H][T]
+    int* mat;                                            // [Bt*H][T][T] (query-major) or nullptr: gP, then gP', then dS' handed from phase to phase
     int T, H, D, GA, blk, limite, kid;
 };
 // statistics slots
@@ -310,24 +314,44 @@ __global__ void __launch_bounds__(256) k_ab_linhas(ArgsTras A) {
     const int emv = max_cabeca<HD>(A.qE, 3 * D / blk, blk, linha0, T, 2 * D + h * HD, red, tid);
     const int nproc = min(T, ((i0 + TI + TJ - 1) / TJ) * TJ);
     const int sh = FASE == 1 ? 0 : desl1(est, A.limite);
-    carrega_alinhado<HD>(a_s, A.gom, A.goE, D, blk, linha0, i0, TI, T, h * HD, emg, GA, tid);
     int mgp = 0;
-    for (int j0 = 0; j0 < nproc; j0 += TJ) {
-        __syncthreads();
-        carrega_alinhado<HD>(b_s, A.qm, A.qE, 3 * D, blk, linha0, j0, TJ, T, 2 * D + h * HD, emv, GA, tid);
-        __syncthreads();
-        int acc[4][4];
-        prod4x4<HD>(a_s, b_s, ty, lane, acc);
+    // With the matrix workspace the product dO . v^T is computed once (phase 1, or phase 2 of the upper-bound variant):
+    // phase 1 leaves gP there, phase 2 replaces it by gP', phase 3 by dS' for the key-tile kernel.
+    int* mat = A.mat ? A.mat + ((size_t)bh * T + i0) * T : nullptr;                // rows i0.. of this (sequence, head)
+    const bool le_mat = mat && (FASE == 3 || (FASE == 2 && !A.limite));
+    if (le_mat) {
 #pragma unroll
-        for (int r = 0; r < 4; r++)
-#pragma unroll
-            for (int c = 0; c < 4; c++) {
-                const int i = i0 + 4 * ty + r, j = j0 + lane + 32 * c;
-                if (j >= nproc) continue;
-                const int g = j <= i ? rnd_d(acc[r][c], sh) : 0;
-                mgp = max(mgp, g < 0 ? -g : g);
-                if (FASE != 1) g_s[(4 * ty + r) * TP + j] = g;
+        for (int r4 = 0; r4 < 4; r4++) {
+            const int r = 4 * ty + r4, i = i0 + r;
+            for (int j = lane; j < nproc; j += 32) {
+                int g = mat[(size_t)r * T + j];
+                if (FASE == 2) {
+                    g = j <= i ? rnd_d(g, sh) : 0;
+                    mgp = max(mgp, g < 0 ? -g : g);
+                }
+                g_s[r * TP + j] = g;
             }
+        }
+    } else {
+        carrega_alinhado<HD>(a_s, A.gom, A.goE, D, blk, linha0, i0, TI, T, h * HD, emg, GA, tid);
+        for (int j0 = 0; j0 < nproc; j0 += TJ) {
+            __syncthreads();
+            carrega_alinhado<HD>(b_s, A.qm, A.qE, 3 * D, blk, linha0, j0, TJ, T, 2 * D + h * HD, emv, GA, tid);
+            __syncthreads();
+            int acc[4][4];
+            prod4x4<HD>(a_s, b_s, ty, lane, acc);
+#pragma unroll
+            for (int r = 0; r < 4; r++)
+#pragma unroll
+                for (int c = 0; c < 4; c++) {
+                    const int i = i0 + 4 * ty + r, j = j0 + lane + 32 * c;
+                    if (j >= nproc) continue;
+                    if (FASE == 1 && mat) mat[(size_t)(4 * ty + r) * T + j] = acc[r][c];
+                    const int g = j <= i ? rnd_d(acc[r][c], sh) : 0;
+                    mgp = max(mgp, g < 0 ? -g : g);
+                    if (FASE != 1) g_s[(4 * ty + r) * TP + j] = g;
+                }
+        }
     }
     if (FASE == 1) {
         max_cta_atomico(mgp, est + S_GP, red, tid);
@@ -356,6 +380,10 @@ __global__ void __launch_bounds__(256) k_ab_linhas(ArgsTras A) {
                 mp = max(mp, p);
             }
         }
+        if (mat)                                  // gP' of this tile for phase 3 and the key-tile kernel
+#pragma unroll
+            for (int r = 0; r < 4; r++)
+                for (int j = lane; j < nproc; j += 32) mat[(size_t)(4 * ty + r) * T + j] = g_s[(4 * ty + r) * TP + j];
         max_cta_atomico(mds, est + S_DS, red, tid);
         if (A.limite) {
             max_cta_atomico(mp, est + S_P, red, tid);
@@ -372,7 +400,11 @@ __global__ void __launch_bounds__(256) k_ab_linhas(ArgsTras A) {
     for (int r = 0; r < 4; r++) {
         int* gr = g_s + (4 * ty + r) * TP;
         const int sl = sl_s[4 * ty + r];
-        for (int j = lane; j < nproc; j += 32) gr[j] = rnd_d((int)pT[j * TI + 4 * ty + r] * (gr[j] - sl), sh2);
+        for (int j = lane; j < nproc; j += 32) {
+            const int ds = rnd_d((int)pT[j * TI + 4 * ty + r] * (gr[j] - sl), sh2);
+            gr[j] = ds;
+            if (mat) mat[(size_t)(4 * ty + r) * T + j] = ds;
+        }
     }
     const int emk = max_cabeca<HD>(A.qE, 3 * D / blk, blk, linha0, T, D + h * HD, red, tid);
     int o[4][4];
@@ -402,7 +434,7 @@ __global__ void __launch_bounds__(256) k_ab_linhas(ArgsTras A) {
 
 // key tiles: gk[j] = sum_i dS'[i][j] q[i], gv[j] = sum_i P[i][j] dO[i].   grid (T/32, Bt*H)
 template <int HD>
-__global__ void __launch_bounds__(256) k_ab_colunas(ArgsTras A) {
+__global__ void __launch_bounds__(256, 2) k_ab_colunas(ArgsTras A) {
     constexpr int PK = HD + 4, ND4 = HD / 4, CP = TJ + 4;
     extern __shared__ __align__(16) int sm[];
     const int T = A.T, H = A.H, D = A.D, GA = A.GA, blk = A.blk;
@@ -420,7 +452,8 @@ __global__ void __launch_bounds__(256) k_ab_colunas(ArgsTras A) {
     const int emq = max_cabeca<HD>(A.qE, 3 * D / blk, blk, linha0, T, h * HD, red, tid);
     const int emv = max_cabeca<HD>(A.qE, 3 * D / blk, blk, linha0, T, 2 * D + h * HD, red, tid);
     const int sh = desl1(est, A.limite), sh2 = desl2(est, A.limite);
-    carrega_alinhado<HD>(a_s, A.qm, A.qE, 3 * D, blk, linha0, j0, TI, T, 2 * D + h * HD, emv, GA, tid);
+    const int* mat = A.mat ? A.mat + (size_t)bh * T * T : nullptr;       // dS' left by phase 3, [i][j]
+    if (!mat) carrega_alinhado<HD>(a_s, A.qm, A.qE, 3 * D, blk, linha0, j0, TI, T, 2 * D + h * HD, emv, GA, tid);
     int gk[4][4], gv[4][4];
 #pragma unroll
     for (int r = 0; r < 4; r++)
@@ -431,21 +464,36 @@ __global__ void __launch_bounds__(256) k_ab_colunas(ArgsTras A) {
         carrega_alinhado<HD>(b_s, A.gom, A.goE, D, blk, linha0, ic, TJ, T, h * HD, emg, GA, tid);
         carrega_alinhado<HD>(c_s, A.qm, A.qE, 3 * D, blk, linha0, ic, TJ, T, h * HD, emq, GA, tid);
         __syncthreads();
-        int acc[4][4];
-        prod4x4<HD>(a_s, b_s, ty, lane, acc);          // acc[r][c] = gP[i = ic + lane + 32 c][j = j0 + 4 ty + r]
-#pragma unroll
-        for (int r = 0; r < 4; r++)
-#pragma unroll
-            for (int c = 0; c < 4; c++) {
-                const int j = j0 + 4 * ty + r, il = lane + 32 * c, i = ic + il;
-                int p = 0, ds = 0;
-                if (i < T && i >= j) {
-                    p = A.P[((size_t)bh * T + j) * T + i];
-                    ds = rnd_d(p * (rnd_d(acc[r][c], sh) - A.sl[(size_t)bh * T + i]), sh2);
-                }
-                ds_c[(4 * ty + r) * CP + il] = ds;
-                p_c[(4 * ty + r) * CP + il] = p;
+        if (mat) {
+            // dS' of the chunk from the workspace: a warp reads the 32 keys of one query row (128 contiguous bytes)
+            for (int il = ty; il < TJ; il += 8) {
+                const int i = ic + il, j = j0 + lane;
+                ds_c[lane * CP + il] = (i < T && i >= j) ? mat[(size_t)i * T + j] : 0;
             }
+#pragma unroll
+            for (int r = 0; r < 4; r++)
+#pragma unroll
+                for (int c = 0; c < 4; c++) {
+                    const int j = j0 + 4 * ty + r, il = lane + 32 * c, i = ic + il;
+                    p_c[(4 * ty + r) * CP + il] = (i < T && i >= j) ? (int)A.P[((size_t)bh * T + j) * T + i] : 0;
+                }
+        } else {
+            int acc[4][4];
+            prod4x4<HD>(a_s, b_s, ty, lane, acc);      // acc[r][c] = gP[i = ic + lane + 32 c][j = j0 + 4 ty + r]
+#pragma unroll
+            for (int r = 0; r < 4; r++)
+#pragma unroll
+                for (int c = 0; c < 4; c++) {
+                    const int j = j0 + 4 * ty + r, il = lane + 32 * c, i = ic + il;
+                    int p = 0, ds = 0;
+                    if (i < T && i >= j) {
+                        p = A.P[((size_t)bh * T + j) * T + i];
+                        ds = rnd_d(p * (rnd_d(acc[r][c], sh) - A.sl[(size_t)bh * T + i]), sh2);
+                    }
+                    ds_c[(4 * ty + r) * CP + il] = ds;
+                    p_c[(4 * ty + r) * CP + il] = p;
+                }
+        }
         __syncthreads();
         const int ni = min(TJ, T - ic);
         acumula4<HD>(ds_c, CP, c_s, 0, ni, ty, lane, gk);
@@ -526,11 +574,12 @@ static int atencao_frente(int blk, const int8_t* qm, const int8_t* qE, int* Oacc
 }
 
 static int atencao_tras_ws(int blk, const int8_t* gom, const int8_t* goE, const int8_t* qm, const int8_t* qE, const uint8_t* P, int* Gacc,
-                           int16_t* Ge, int Bt, int T, int H, int D, int GA, int limite, int kid, cudaStream_t st, int* ws) {
+                           int16_t* Ge, int Bt, int T, int H, int D, int GA, int limite, int kid, cudaStream_t st, int* ws, bool com_matriz) {
     int hd, lg2;
     if (!at_valido(blk, Bt, T, H, D, &hd, &lg2)) return (int)cudaErrorInvalidValue;
     const int BH = Bt * H;
-    at::ArgsTras A = {gom, goE, qm, qE, P, Gacc, Ge, ws, ws + (size_t)BH * at::N_EST, T, H, D, GA, blk, limite, kid};
+    at::ArgsTras A = {gom, goE, qm, qE, P, Gacc, Ge, ws, ws + (size_t)BH * at::N_EST, com_matriz ? ws + (size_t)BH * (at::N_EST + T) : nullptr,
+                      T, H, D, GA, blk, limite, kid};
     cudaError_t c = cudaMemsetAsync(ws, 0, (size_t)BH * at::N_EST * sizeof(int), st);
     if (c != cudaSuccess) return (int)c;
     const dim3 grade(T / at::TI, BH);
@@ -556,7 +605,11 @@ static int atencao_tras_ws(int blk, const int8_t* gom, const int8_t* goE, const 
 static int atencao_tras(int blk, const int8_t* gom, const int8_t* goE, const int8_t* qm, const int8_t* qE, const uint8_t* P, int* Gacc,
                         int16_t* Ge, int Bt, int T, int H, int D, int GA, int limite, int kid, cudaStream_t st) {
     if (Bt <= 0 || T <= 0 || H <= 0) return (int)cudaErrorInvalidValue;
-    const size_t precisa = (size_t)Bt * H * (at::N_EST + T);
+    // statistics and s_lin, plus the T x T matrix per (sequence, head) that carries gP / gP' / dS' between the phases
+    // (1 GiB at most; beyond that the phases recompute instead)
+    const size_t base = (size_t)Bt * H * (at::N_EST + T), matriz = (size_t)Bt * H * T * T;
+    const bool com_matriz = matriz <= ((size_t)1 << 28);
+    const size_t precisa = base + (com_matriz ? matriz : 0);
     if (precisa > g_at_ws_ints) {
         if (g_at_ws) cudaFree(g_at_ws);
         g_at_ws = nullptr;
@@ -565,7 +618,7 @@ static int atencao_tras(int blk, const int8_t* gom, const int8_t* goE, const int
         if (c != cudaSuccess) return (int)c;
         g_at_ws_ints = precisa;
     }
-    return atencao_tras_ws(blk, gom, goE, qm, qE, P, Gacc, Ge, Bt, T, H, D, GA, limite, kid, st, g_at_ws);
+    return atencao_tras_ws(blk, gom, goE, qm, qE, P, Gacc, Ge, Bt, T, H, D, GA, limite, kid, st, g_at_ws, com_matriz);
 }
 
 }  // namespace jt

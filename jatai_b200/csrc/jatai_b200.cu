@@ -361,7 +361,8 @@ int jt_atencao_back_fixo(const void* gom, const void* goE, const void* qm, const
         g_at_fixo_end[dev] = static_cast<int*>(p);
     }
     return atencao_tras_ws(g_blk, (const int8_t*)gom, (const int8_t*)goE, (const int8_t*)qm, (const int8_t*)qE, (const uint8_t*)P, (int*)Gacc,
-                           (int16_t*)Ge, Bt, T, H, D, GA, limite, kid, g_stream, g_at_fixo_end[dev]);
+                           (int16_t*)Ge, Bt, T, H, D, GA, limite, kid, g_stream, g_at_fixo_end[dev],
+                           precisa + (size_t)Bt * H * T * T <= JT_FIXO_INTS);      // room for the T x T matrices too, or the phases recompute
 }
 
 // The 16-bit residual stream of the reference (jt_para16 / jt_para8 / jt_soma16) is an opt-in ablation without an

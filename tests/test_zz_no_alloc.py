@@ -26,7 +26,7 @@ def test_atencao_back_sem_alocar():
     lib = oc.lib
     lib.jt_atencao_back_fixo.restype = ctypes.c_int
     reg.novo_passo(0)
-    for n, (Bt, T, H, D, limite) in enumerate([(2, 128, 2, 128, 0), (1, 256, 8, 128, 1), (2, 128, 2, 128, 0)]):
+    for n, (Bt, T, H, D, limite) in enumerate([(2, 128, 2, 128, 0), (1, 256, 8, 128, 1), (2, 512, 8, 128, 0), (2, 512, 8, 128, 1), (2, 128, 2, 128, 0)]):
         G = casos.Gen(900 + n, 32)
         M = Bt * T
         qkv = tuple(t.cuda() for t in G.bloco(M, 3 * D, espalha=5, zera=0.05))
