@@ -112,15 +112,17 @@ class Modelo:
         self._feitos.add(n)
         self._pendente = None
 
-    def _gemms_adiados(self, maximos):
-        """Data parallel, after the MAX collective: every weight-gradient GEMM with the global row maxima.  The GEMMs
-        are independent of each other, so on the GPU they are dealt round-robin to a few streams (parallel branches
-        of the CUDA graph when recording) and joined at the end."""
+    def _gemms_adiados(self, maximos, inicio=0, fim=None):
+        """Data parallel, after the MAX collective: the weight-gradient GEMMs [inicio, fim) of the deferred list (all of
+        them by default) with the global row maxima.  The GEMMs are independent of each other, so on the GPU they are
+        dealt round-robin to a few streams (parallel branches of the CUDA graph when recording) and joined at the end.
+        The list is cleared when its last GEMM has been issued."""
         ops = self.ops
+        fim = len(self._adiados) if fim is None else fim
         principal = torch.cuda.current_stream() if self._ramos else None
         for r in self._ramos:
             r.wait_stream(principal)
-        for i, ((nome, a, b, _, _), (RA, RB)) in enumerate(zip(self._adiados, maximos)):
+        for i, ((nome, a, b, _, _), (RA, RB)) in enumerate(zip(self._adiados[inicio:fim], maximos[inicio:fim])):
             with self.reg.trecho(nome):
                 if not self._ramos:
                     self._grads[nome] = ops.gemm(a, b, cru=True, RA=RA, RB=RB)
@@ -136,7 +138,8 @@ class Modelo:
                         ops.lib.jt_stream(principal.cuda_stream)
         for r in self._ramos:
             principal.wait_stream(r)
-        self._adiados = []
+        if fim == len(self._adiados):
+            self._adiados = []
 
     def _otimiza(self, grads, k_lr):
         ops = self.ops
@@ -250,9 +253,12 @@ class PassoGravado:
     recording is kept: the launch ids are baked into the kernel arguments, so a sentinel raised during a replay
     names the same operation and section as it would in eager mode.  Run one eager step before recording (the
     attention backward sizes its workspace on first use, which a capture does not allow).  Data parallel: the
-    step is recorded as three graphs (forward+backward | deferred weight-gradient GEMMs | optimiser) and the two
-    collectives run eagerly between the replays, on the same stream.
+    step is recorded as 1 + 2 GRUPOS graphs (forward+backward | per group of weights: deferred weight-gradient GEMMs
+    | optimiser) and the collectives run eagerly between the replays: one MAX for the whole step, then one SUM per
+    group, which overlaps the next group's GEMMs while the group's optimiser step follows on a second stream.
     """
+
+    GRUPOS = 4          # data parallel: pieces the weight-gradient tail (GEMMs | SUM collective | optimiser) is pipelined in
 
     def __init__(self, modelo, Bt, T, k_lr):
         self.m, self.reg, self.k_lr = modelo, modelo.reg, k_lr
@@ -276,20 +282,43 @@ class PassoGravado:
                 # their final sizes (one eager step has run), so the graphs see fixed addresses.
                 assert getattr(red, "_max", None) is not None and getattr(red, "_plano", None) is not None, \
                     "run one eager data-parallel step before recording"
-                self.grafos = [torch.cuda.CUDAGraph() for _ in range(3)]
-                with torch.cuda.graph(self.grafos[0]):
+                g0 = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g0):
                     lib.jt_stream(torch.cuda.current_stream().cuda_stream)
                     self.perda = modelo.frente_tras(self.tok, self.alvo)
                     pares = [(ra, rb) for _, _, _, ra, rb in modelo._adiados]
                     red.empacota_maximos(pares)
-                with torch.cuda.graph(self.grafos[1], pool=self.grafos[0].pool()):
-                    lib.jt_stream(torch.cuda.current_stream().cuda_stream)
-                    modelo._gemms_adiados(red.vistas_maximos(pares))
-                    vistas = red.empacota_somas(modelo._grads)
-                with torch.cuda.graph(self.grafos[2], pool=self.grafos[0].pool()):
-                    lib.jt_stream(torch.cuda.current_stream().cuda_stream)
-                    with self.reg.trecho("otimizador"):
-                        modelo._otimiza(vistas, k_lr)
+                # The tail is cut into groups of consecutive weights: while group g's sums cross the wire, group
+                # g+1's GEMMs run, and group g's optimiser step runs on a second stream as soon as its sums are in.
+                # The GEMM graphs share graph 0's pool (replayed in recording order on one stream); the optimiser
+                # graphs have a pool of their own (they run beside the GEMM graphs).
+                n = len(pares)
+                ng = min(self.GRUPOS, n)
+                cortes = [n * g // ng for g in range(ng + 1)]
+                maximos = red.vistas_maximos(pares)
+                nomes = [a[0] for a in modelo._adiados]
+                self._gemm, self._otim, self._fatias, vistas_g = [], [], [], []
+                for g in range(ng):
+                    gg = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(gg, pool=g0.pool()):
+                        lib.jt_stream(torch.cuda.current_stream().cuda_stream)
+                        modelo._gemms_adiados(maximos, cortes[g], cortes[g + 1])
+                        v, fatia = red.empacota_grupo({k: modelo._grads[k] for k in nomes[cortes[g]:cortes[g + 1]]}, modelo._grads)
+                    self._gemm.append(gg)
+                    self._fatias.append(fatia)
+                    vistas_g.append(v)
+                self._vivos = (vistas_g, dict(modelo._grads))        # keeps every tensor the graphs read at its address
+                self._lado = torch.cuda.Stream(device=modelo.dev)
+                pool_o = None
+                for g in range(ng):
+                    go = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(go, **({} if pool_o is None else {"pool": pool_o})):
+                        lib.jt_stream(torch.cuda.current_stream().cuda_stream)
+                        with self.reg.trecho("otimizador"):
+                            modelo._otimiza(vistas_g[g], k_lr)
+                    pool_o = go.pool()
+                    self._otim.append(go)
+                self.grafos = [g0] + self._gemm + self._otim
         finally:
             lib.jt_stream(None)
             modelo.estatisticas, self.reg.vigiar, self.reg.perfil = est, vig, perf
@@ -304,9 +333,16 @@ class PassoGravado:
             self.grafos[0].replay()
         else:
             red = self.m.redutor
+            principal = torch.cuda.current_stream()
             self.grafos[0].replay()
             red.reduz_maximos()
-            self.grafos[1].replay()
-            red.reduz_somas()
-            self.grafos[2].replay()
+            for g, (gg, go, fatia) in enumerate(zip(self._gemm, self._otim, self._fatias)):
+                gg.replay()
+                pronto = red.reduz_fatia(*fatia)                  # asynchronous: ordered after this group's GEMMs
+                if g == 0:
+                    self._lado.wait_stream(principal)             # the optimiser may not overtake the backward's last read of a weight
+                with torch.cuda.stream(self._lado):
+                    pronto.wait()
+                    go.replay()
+            principal.wait_stream(self._lado)
         return self.perda

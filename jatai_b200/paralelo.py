@@ -84,6 +84,7 @@ class Redutor:
         algum = next(iter(grads.values()))[0]
         if getattr(self, "_plano", None) is None or self._plano.numel() != total or self._plano.device != algum.device:
             self._plano = torch.empty(total, dtype=torch.int32, device=algum.device)
+        self._total_plano = total
         o, vistas = 0, {}
         for n, (acc, e) in grads.items():
             v = self._plano[o:o + acc.numel()].view(acc.shape)
@@ -91,6 +92,32 @@ class Redutor:
             vistas[n] = (v, e)
             o += acc.numel()
         return vistas
+
+    def empacota_grupo(self, grupo, todos):
+        """empacota_somas for one group of consecutive gradients.  `todos` fixes the layout of the flat buffer: it holds,
+        in order, every gradient up to and including this group (later ones are not needed to place it).  Returns the
+        group's views and its (start, end) in the buffer, which an eager step has already sized."""
+        total = getattr(self, "_total_plano", None)
+        assert getattr(self, "_plano", None) is not None and total is not None, "run one eager data-parallel step first"
+        nomes = list(todos.keys())
+        primeiro = nomes.index(next(iter(grupo)))
+        o = sum(todos[n][0].numel() for n in nomes[:primeiro])
+        o0, vistas = o, {}
+        for n, (acc, e) in grupo.items():
+            v = self._plano[o:o + acc.numel()].view(acc.shape)
+            v.copy_(acc)
+            vistas[n] = (v, e)
+            o += acc.numel()
+        assert o <= total
+        return vistas, (o0, o)
+
+    def reduz_fatia(self, o0, o1):
+        """SUM over ranks of one slice of the flat buffer, asynchronously: returns the work handle; `wait()` on it makes
+        the then-current stream wait for the result."""
+        w = dist.all_reduce(self._plano[o0:o1], op=dist.ReduceOp.SUM, group=self.grupo, async_op=True)
+        self.bytes_soma += (o1 - o0) * 4
+        self.chamadas += 1
+        return w
 
     def reduz_somas(self):
         dist.all_reduce(self._plano, op=dist.ReduceOp.SUM, group=self.grupo)
