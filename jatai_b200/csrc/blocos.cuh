@@ -308,7 +308,8 @@ __global__ void __launch_bounds__(256) k_transpoe(const int8_t* __restrict__ X, 
 }
 
 // Transposition for block 32, wide tiles: TR (32, 64 or 128) rows x 256 columns per CTA of 2 TR threads; the launcher
-// takes the tallest tile that still gives every SM a CTA.  A thread owns a 32-row block of 4
+// takes the tallest tile that still gives every SM a CTA (and, for the smallest matrices, a thread per column instead
+// of per word: CPT = 1).  A thread owns a 32-row block of 4
 // adjacent columns (one 32-bit word per row) and quantises the 4 new blocks without leaving its registers.
 // The quantiser runs in fp32, exactly: a mantissa times 2^(e - eref) is exact in fp32, the largest magnitude gives
 // top = max(e + bitlen(v)) through its exponent field, and one FFMA against 1.5*2^23 rounds v * 2^(e - E) half to
@@ -330,27 +331,30 @@ __device__ __noinline__ void transpoe32_lento(const uint32_t (*tile)[T32_PW], co
     *Edst = (int8_t)Eo;
 }
 
-template <int TR>
-__global__ void __launch_bounds__(2 * TR, 256 / TR) k_transpoe32(const int8_t* __restrict__ X, const int8_t* __restrict__ EX, int8_t* __restrict__ Y,
-                                                                 int8_t* __restrict__ EY, int R, int C, int kid) {
-    constexpr int TC = 256, PW = T32_PW, NT = 2 * TR;
+template <int TR, int CPT = 4>
+__global__ void __launch_bounds__(8 * TR / CPT, 512 / (8 * TR / CPT)) k_transpoe32(const int8_t* __restrict__ X, const int8_t* __restrict__ EX,
+                                                                                   int8_t* __restrict__ Y, int8_t* __restrict__ EY, int R, int C,
+                                                                                   int kid) {
+    static_assert(CPT == 4 || CPT == 1, "a thread owns the 4 columns of a word or one of them");
+    constexpr int TC = 256, PW = T32_PW, NT = 8 * TR / CPT;
     __shared__ uint32_t tile[TR][PW];
     __shared__ __align__(4) int8_t et[TR][8];
     const int r0 = blockIdx.y * TR, c0 = blockIdx.x * TC;
-    const int tid = threadIdx.x, wp = tid >> 5, lane = tid & 31;
+    const int tid = threadIdx.x;
     const int nbx = C / 32, nby = R / 32;
 #pragma unroll
-    for (int k = 0; k < 8; k++) {
+    for (int k = 0; k < TR * 16 / NT; k++) {
         const int idx = tid + NT * k, lr = idx >> 4, c16 = idx & 15;
         const uint4 v = *reinterpret_cast<const uint4*>(X + (size_t)(r0 + lr) * C + c0 + c16 * 16);
         tile[lr][c16 * 4] = v.x; tile[lr][c16 * 4 + 1] = v.y; tile[lr][c16 * 4 + 2] = v.z; tile[lr][c16 * 4 + 3] = v.w;
     }
-    {
+    if (tid < 2 * TR) {
         const int lr = tid >> 1, k4 = (tid & 1) * 4;
         *reinterpret_cast<uint32_t*>(&et[lr][k4]) = *reinterpret_cast<const uint32_t*>(EX + (size_t)(r0 + lr) * nbx + c0 / 32 + k4);
     }
     __syncthreads();
-    const int rb = wp >> 1, cw = lane + 32 * (wp & 1);              // 32-row block, word column
+    // word column, 32-row block and (CPT = 1: small matrices, four times the threads) the byte of the word
+    const int cw = tid & 63, rb = CPT == 4 ? tid >> 6 : tid >> 8, k_meu = (tid >> 6) & 3;
     uint32_t w[32];
     float A[32];
     int eref = -128, emin = 127;
@@ -366,6 +370,7 @@ __global__ void __launch_bounds__(2 * TR, 256 / TR) k_transpoe32(const int8_t* _
     const bool largo = eref - emin > 100;                           // spread too wide for the fp32 path
 #pragma unroll
     for (int k = 0; k < 4; k++) {
+        if (CPT == 1 && k != k_meu) continue;
         const size_t col = (size_t)(c0 + 4 * cw + k);
         int8_t* dst = Y + col * R + r0 + rb * 32;
         int8_t* Edst = EY + col * nby + (r0 + rb * 32) / 32;

@@ -254,7 +254,8 @@ int jt_transpoe(const void* X, const void* EX, void* Y, void* EY, int R, int C, 
 #define ARGS (const int8_t*)X, (const int8_t*)EX, (int8_t*)Y, (int8_t*)EY, R, C, kid
         if (t128 >= 148) k_transpoe32<128><<<dim3(C / 256, R / 128), 256, 0, g_stream>>>(ARGS);
         else if (2 * t128 >= 148) k_transpoe32<64><<<dim3(C / 256, R / 64), 128, 0, g_stream>>>(ARGS);
-        else k_transpoe32<32><<<dim3(C / 256, R / 32), 64, 0, g_stream>>>(ARGS);
+        else if (4 * t128 >= 296) k_transpoe32<32><<<dim3(C / 256, R / 32), 64, 0, g_stream>>>(ARGS);
+        else k_transpoe32<32, 1><<<dim3(C / 256, R / 32), 256, 0, g_stream>>>(ARGS);
 #undef ARGS
         return fim();
     }
