@@ -100,11 +100,6 @@ __device__ __forceinline__ int warp_sum(int v) {
     for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(FULL, v, o);
     return v;
 }
-__device__ __forceinline__ long long warp_sum64(long long v) {
-#pragma unroll
-    for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(FULL, v, o);
-    return v;
-}
 
 // ---------------------------------------------------------------------------------------- 16-byte vectors
 // A thread of the bandwidth kernels owns 16 consecutive elements: one 128-bit access of int8 data.

@@ -277,3 +277,37 @@ def test_gemm_largura_do_tile(amb, nome, blk, f, tn):
         compara(f"{nome} tn {tn}", outs, casos.roda(spec.Spec(blk), op, args, kw))
     finally:
         oc.lib.jt_gemm_tn(0)
+
+
+@pytest.mark.parametrize("tn", [64, 128])
+@pytest.mark.parametrize("caso", ["expoentes afastados", "linhas nulas", "acumuladores grandes"])
+@pytest.mark.parametrize("op", ["gemm", "gemm_soma", "gemm_relu2", "gemm_relu2_back"])
+def test_gemm_estagio_de_saida(amb, op, caso, tn):
+    """The output stage of the tensor-core GEMM quantises in fp32 when that is exact and in integers otherwise.  These
+    inputs force the integer side: column exponents of one block more than 64 apart, all-zero rows of B (row maximum
+    -127 next to ordinary rows), accumulators at or above 2^24 - each against the specification."""
+    ops, oc, reg = amb
+    ops.define_blk(32)
+    oc.lib.jt_gemm_via(0)
+    assert oc.lib.jt_gemm_tn(tn) == 0
+    try:
+        reg.novo_passo(0)
+        G = casos.Gen(4242, 32)
+        M, K, N = 256, 512, 256
+        A, B = G.bloco(M, K, espalha=2), G.bloco(N, K, espalha=2)
+        if caso == "expoentes afastados":
+            B[1][0::2] -= 50                      # even rows of B 70 exponents below the odd ones, inside every block of columns
+            B[1][1::2] += 20                      # (output exponents stay far from the int8 limits, squared too)
+        elif caso == "linhas nulas":
+            B[0][::3] = 0
+            B[1][::3] = -127
+        else:
+            A = (torch.full_like(A[0], 127), torch.full_like(A[1], -8))
+            B = (torch.full_like(B[0], 127), torch.full_like(B[1], -8))
+        X = G.bloco(M, N, espalha=3)
+        args = {"gemm": (A, B), "gemm_soma": (A, B, X), "gemm_relu2": (A, B), "gemm_relu2_back": (A, B, X)}[op]
+        outs = casos.roda(oc, op, tuple(para_gpu(a) for a in args), {})
+        torch.cuda.synchronize()
+        compara(f"{op} {caso} tn {tn}", outs, casos.roda(spec.Spec(32), op, args, {}))
+    finally:
+        oc.lib.jt_gemm_tn(0)
