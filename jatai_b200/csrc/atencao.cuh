@@ -83,25 +83,34 @@ __device__ __forceinline__ void carrega_alinhado(int* dst, const int8_t* __restr
 }
 
 // acc[r][c] = sum_d a_s[4 ty + r][d] * b_s[lane + 32 c][d]   (exact; |operands| <= 2032, hd <= 64)
-template <int HD>
-__device__ __forceinline__ void prod4x4(const int* a_s, const int* b_s, int ty, int lane, int (&acc)[4][4]) {
+// Only the first NC blocks of 32 rows of b_s are multiplied (the rest of acc stays 0): a causal row tile needs no
+// product with the key blocks beyond its diagonal.
+template <int HD, int NC>
+__device__ __forceinline__ void prod4xn(const int* a_s, const int* b_s, int ty, int lane, int (&acc)[4][4]) {
     constexpr int PK = HD + 4;
+#pragma unroll
+    for (int d4 = 0; d4 < HD / 4; d4++) {
+        int4 a[4], b[NC];
+#pragma unroll
+        for (int r = 0; r < 4; r++) a[r] = *reinterpret_cast<const int4*>(a_s + (4 * ty + r) * PK + 4 * d4);
+#pragma unroll
+        for (int c = 0; c < NC; c++) b[c] = *reinterpret_cast<const int4*>(b_s + (lane + 32 * c) * PK + 4 * d4);
+#pragma unroll
+        for (int r = 0; r < 4; r++)
+#pragma unroll
+            for (int c = 0; c < NC; c++) acc[r][c] += a[r].x * b[c].x + a[r].y * b[c].y + a[r].z * b[c].z + a[r].w * b[c].w;
+    }
+}
+template <int HD>
+__device__ __forceinline__ void prod4x4(const int* a_s, const int* b_s, int ty, int lane, int (&acc)[4][4], int nblocos = 4) {
 #pragma unroll
     for (int r = 0; r < 4; r++)
 #pragma unroll
         for (int c = 0; c < 4; c++) acc[r][c] = 0;
-#pragma unroll
-    for (int d4 = 0; d4 < HD / 4; d4++) {
-        int4 a[4], b[4];
-#pragma unroll
-        for (int r = 0; r < 4; r++) a[r] = *reinterpret_cast<const int4*>(a_s + (4 * ty + r) * PK + 4 * d4);
-#pragma unroll
-        for (int c = 0; c < 4; c++) b[c] = *reinterpret_cast<const int4*>(b_s + (lane + 32 * c) * PK + 4 * d4);
-#pragma unroll
-        for (int r = 0; r < 4; r++)
-#pragma unroll
-            for (int c = 0; c < 4; c++) acc[r][c] += a[r].x * b[c].x + a[r].y * b[c].y + a[r].z * b[c].z + a[r].w * b[c].w;
-    }
+    if (nblocos >= 4) prod4xn<HD, 4>(a_s, b_s, ty, lane, acc);
+    else if (nblocos == 3) prod4xn<HD, 3>(a_s, b_s, ty, lane, acc);
+    else if (nblocos == 2) prod4xn<HD, 2>(a_s, b_s, ty, lane, acc);
+    else prod4xn<HD, 1>(a_s, b_s, ty, lane, acc);
 }
 
 // Row products: out[r][d] = sum_j w_s[4 ty + r][j0 + j] * v_s[j][d] for the 4 rows of warp ty (P.V, dS'.k, dS'^T.q, P^T.dO).
@@ -185,7 +194,7 @@ __global__ void __launch_bounds__(256) k_atencao(const int8_t* __restrict__ qm, 
         carrega_alinhado<HD>(kv_s, qm, qE, ld, blk, linha0, j0, TJ, T, D + h * HD, emk, GA, tid);
         __syncthreads();
         int acc[4][4];
-        prod4x4<HD>(q_s, kv_s, ty, lane, acc);
+        prod4x4<HD>(q_s, kv_s, ty, lane, acc, (i0 + TI - j0 + 31) / 32);       // key blocks up to the diagonal
 #pragma unroll
         for (int r = 0; r < 4; r++)
 #pragma unroll
@@ -237,7 +246,7 @@ __global__ void __launch_bounds__(256) k_atencao(const int8_t* __restrict__ qm, 
         __syncthreads();
         carrega_alinhado<HD>(kv_s, qm, qE, ld, blk, linha0, j0, TJ, T, 2 * D + h * HD, emv, GA, tid);
         __syncthreads();
-        acumula4<HD>(u_s, TP, kv_s, j0, min(TJ, nproc - j0), ty, lane, o);
+        acumula4<HD>(u_s, TP, kv_s, j0, min(TJ, i0 + TI - j0), ty, lane, o);     // P is zero beyond the diagonal
     }
     acumula4_fim<HD>(o);
     if (lane < ND4) {
@@ -339,7 +348,7 @@ __global__ void __launch_bounds__(256) k_ab_linhas(ArgsTras A) {
             carrega_alinhado<HD>(b_s, A.qm, A.qE, 3 * D, blk, linha0, j0, TJ, T, 2 * D + h * HD, emv, GA, tid);
             __syncthreads();
             int acc[4][4];
-            prod4x4<HD>(a_s, b_s, ty, lane, acc);
+            prod4x4<HD>(a_s, b_s, ty, lane, acc, (i0 + TI - j0 + 31) / 32);
 #pragma unroll
             for (int r = 0; r < 4; r++)
 #pragma unroll
@@ -416,7 +425,7 @@ __global__ void __launch_bounds__(256) k_ab_linhas(ArgsTras A) {
         __syncthreads();
         carrega_alinhado<HD>(b_s, A.qm, A.qE, 3 * D, blk, linha0, j0, TJ, T, D + h * HD, emk, GA, tid);
         __syncthreads();
-        acumula4<HD>(g_s, TP, b_s, j0, min(TJ, nproc - j0), ty, lane, o);
+        acumula4<HD>(g_s, TP, b_s, j0, min(TJ, i0 + TI - j0), ty, lane, o);      // dS' is zero beyond the diagonal
     }
     acumula4_fim<HD>(o);
     if (lane < ND4) {
@@ -495,9 +504,9 @@ __global__ void __launch_bounds__(256, 2) k_ab_colunas(ArgsTras A) {
                 }
         }
         __syncthreads();
-        const int ni = min(TJ, T - ic);
-        acumula4<HD>(ds_c, CP, c_s, 0, ni, ty, lane, gk);
-        acumula4<HD>(p_c, CP, b_s, 0, ni, ty, lane, gv);
+        const int ni = min(TJ, T - ic), pula = max(j0 - ic, 0);       // queries before the key tile see none of its keys
+        acumula4<HD>(ds_c, CP, c_s + pula * PK, pula, ni - pula, ty, lane, gk);
+        acumula4<HD>(p_c, CP, b_s + pula * PK, pula, ni - pula, ty, lane, gv);
     }
     acumula4_fim<HD>(gk);
     acumula4_fim<HD>(gv);
