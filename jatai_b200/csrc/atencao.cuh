@@ -191,7 +191,7 @@ __global__ void __launch_bounds__(256) k_atencao(const int8_t* __restrict__ qm, 
     int mx[4] = {U_MIN, U_MIN, U_MIN, U_MIN};
     for (int j0 = 0; j0 < nproc; j0 += TJ) {
         __syncthreads();
-        carrega_alinhado<HD>(kv_s, qm, qE, ld, blk, linha0, j0, TJ, T, D + h * HD, emk, GA, tid);
+        carrega_alinhado<HD>(kv_s, qm, qE, ld, blk, linha0, j0, min(TJ, i0 + TI - j0), T, D + h * HD, emk, GA, tid);     // keys up to the diagonal
         __syncthreads();
         int acc[4][4];
         prod4x4<HD>(q_s, kv_s, ty, lane, acc, (i0 + TI - j0 + 31) / 32);       // key blocks up to the diagonal
@@ -244,7 +244,7 @@ __global__ void __launch_bounds__(256) k_atencao(const int8_t* __restrict__ qm, 
         for (int k = 0; k < 4; k++) o[r][k] = 0;
     for (int j0 = 0; j0 < nproc; j0 += TJ) {
         __syncthreads();
-        carrega_alinhado<HD>(kv_s, qm, qE, ld, blk, linha0, j0, TJ, T, 2 * D + h * HD, emv, GA, tid);
+        carrega_alinhado<HD>(kv_s, qm, qE, ld, blk, linha0, j0, min(TJ, i0 + TI - j0), T, 2 * D + h * HD, emv, GA, tid);
         __syncthreads();
         acumula4<HD>(u_s, TP, kv_s, j0, min(TJ, i0 + TI - j0), ty, lane, o);     // P is zero beyond the diagonal
     }
@@ -345,7 +345,7 @@ __global__ void __launch_bounds__(256) k_ab_linhas(ArgsTras A) {
         carrega_alinhado<HD>(a_s, A.gom, A.goE, D, blk, linha0, i0, TI, T, h * HD, emg, GA, tid);
         for (int j0 = 0; j0 < nproc; j0 += TJ) {
             __syncthreads();
-            carrega_alinhado<HD>(b_s, A.qm, A.qE, 3 * D, blk, linha0, j0, TJ, T, 2 * D + h * HD, emv, GA, tid);
+            carrega_alinhado<HD>(b_s, A.qm, A.qE, 3 * D, blk, linha0, j0, min(TJ, i0 + TI - j0), T, 2 * D + h * HD, emv, GA, tid);
             __syncthreads();
             int acc[4][4];
             prod4x4<HD>(a_s, b_s, ty, lane, acc, (i0 + TI - j0 + 31) / 32);
@@ -423,7 +423,7 @@ __global__ void __launch_bounds__(256) k_ab_linhas(ArgsTras A) {
         for (int k = 0; k < 4; k++) o[r][k] = 0;
     for (int j0 = 0; j0 < nproc; j0 += TJ) {
         __syncthreads();
-        carrega_alinhado<HD>(b_s, A.qm, A.qE, 3 * D, blk, linha0, j0, TJ, T, D + h * HD, emk, GA, tid);
+        carrega_alinhado<HD>(b_s, A.qm, A.qE, 3 * D, blk, linha0, j0, min(TJ, i0 + TI - j0), T, D + h * HD, emk, GA, tid);
         __syncthreads();
         acumula4<HD>(g_s, TP, b_s, j0, min(TJ, i0 + TI - j0), ty, lane, o);      // dS' is zero beyond the diagonal
     }
@@ -470,8 +470,9 @@ __global__ void __launch_bounds__(256, 2) k_ab_colunas(ArgsTras A) {
         for (int k = 0; k < 4; k++) gk[r][k] = gv[r][k] = 0;
     for (int ic = (j0 / TJ) * TJ; ic < T; ic += TJ) {
         __syncthreads();
-        carrega_alinhado<HD>(b_s, A.gom, A.goE, D, blk, linha0, ic, TJ, T, h * HD, emg, GA, tid);
-        carrega_alinhado<HD>(c_s, A.qm, A.qE, 3 * D, blk, linha0, ic, TJ, T, h * HD, emq, GA, tid);
+        const int antes = mat ? max(j0 - ic, 0) : 0;          // query rows before the key tile are not needed (the recomputing path reads them)
+        carrega_alinhado<HD>(b_s + antes * PK, A.gom, A.goE, D, blk, linha0, ic + antes, TJ - antes, T, h * HD, emg, GA, tid);
+        carrega_alinhado<HD>(c_s + antes * PK, A.qm, A.qE, 3 * D, blk, linha0, ic + antes, TJ - antes, T, h * HD, emq, GA, tid);
         __syncthreads();
         if (mat) {
             // dS' of the chunk from the workspace: a warp reads the 32 keys of one query row (128 contiguous bytes)
