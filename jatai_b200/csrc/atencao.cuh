@@ -186,7 +186,7 @@ __global__ void __launch_bounds__(256) k_atencao(const int8_t* __restrict__ qm, 
     const int emv = max_cabeca<HD>(qE, ldb, blk, linha0, T, 2 * D + h * HD, red, tid);
     const int s_u = -((emq - GA) + (emk - GA) - lg2 / 2 + 8);
     const int incl = incl_alibi(h);
-    const int nproc = min(T, ((i0 + TI + TJ - 1) / TJ) * TJ);          // keys this tile looks at (multiple of 32)
+    const int nproc = i0 + TI;                                         // keys this tile looks at: up to its diagonal (multiple of 32)
     carrega_alinhado<HD>(q_s, qm, qE, ld, blk, linha0, i0, TI, T, h * HD, emq, GA, tid);
     int mx[4] = {U_MIN, U_MIN, U_MIN, U_MIN};
     for (int j0 = 0; j0 < nproc; j0 += TJ) {
@@ -321,7 +321,7 @@ __global__ void __launch_bounds__(256) k_ab_linhas(ArgsTras A) {
     int* est = A.est + bh * N_EST;
     const int emg = max_cabeca<HD>(A.goE, D / blk, blk, linha0, T, h * HD, red, tid);
     const int emv = max_cabeca<HD>(A.qE, 3 * D / blk, blk, linha0, T, 2 * D + h * HD, red, tid);
-    const int nproc = min(T, ((i0 + TI + TJ - 1) / TJ) * TJ);
+    const int nproc = i0 + TI;                      // keys up to the diagonal of this row tile
     const int sh = FASE == 1 ? 0 : desl1(est, A.limite);
     int mgp = 0;
     // With the matrix workspace the product dO . v^T is computed once (phase 1, or phase 2 of the upper-bound variant):
