@@ -194,7 +194,8 @@ __global__ void __launch_bounds__(256) k_momento(const int* __restrict__ gacc, c
     for (int i = 0; i < 16; i++) {
         if (g[i] >= LIM || g[i] <= -LIM) reporta(E_ACUM, kid, o + i, g[i], eg[i]);
         const int ec = max(em + 10, eg[i] + bitlen(g[i])) - 28;
-        v[i] = rnd(mm[i] * 7, ec - em, kid, o + i) + rnd(g[i], ec - eg[i], kid, o + i);
+        // left shifts cannot lose bits here: |7 m| < 2^10 moves up by at most 18, g by at most 28 - bitlen(g)
+        v[i] = desloca(mm[i] * 7, ec - em) + desloca(g[i], ec - eg[i]);
         ee[i] = ec;
     }
     const int Eo = quant_geral<16, BLK / 16>(v, ee, q, kid, o);
@@ -218,16 +219,17 @@ __global__ void __launch_bounds__(256) k_peso(int8_t* __restrict__ Wm, int8_t* _
     }
     const int ew = WE[w], em = (int)ME[w] - k_lr, er = ef ? (int)RE[w] : E_ZERO;
     const int ec = max(max(ew + 7, em + 7), er + 7) - 27;
+    // every operand is a mantissa (7 bits) moved up by at most 20: the left shifts cannot lose bits
 #pragma unroll
     for (int i = 0; i < 16; i++)
-        alvo[i] = rnd(wv[i], ec - ew, kid, o + i) - rnd(mv[i], ec - em, kid, o + i) + (ef ? rnd(rv[i], ec - er, kid, o + i) : 0);
+        alvo[i] = desloca(wv[i], ec - ew) - desloca(mv[i], ec - em) + (ef ? desloca(rv[i], ec - er) : 0);
     const int Ew = quant_uniforme<16, BLK / 16>(alvo, ec, q, kid, o);
     if (ativo) grava16(Wm + o, q);
     if (lider) WE[w] = (int8_t)Ew;
     if (!ef) return;
     int dif[16], r[16];
 #pragma unroll
-    for (int i = 0; i < 16; i++) dif[i] = alvo[i] - (q[i] == 0 ? 0 : rnd(q[i], ec - Ew, kid, o + i));
+    for (int i = 0; i < 16; i++) dif[i] = alvo[i] - desloca(q[i], ec - Ew);          // q 2^(Ew - ec) stays below the 2^30 of alvo's range
     const int Er = quant_uniforme<16, BLK / 16>(dif, ec, r, kid, o);
     if (ativo) grava16(Rm + o, r);
     if (lider) RE[w] = (int8_t)Er;
