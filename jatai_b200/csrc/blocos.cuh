@@ -522,7 +522,8 @@ __global__ void __launch_bounds__(256) k_rms_back(const int8_t* __restrict__ gm,
         int v[16], e[16], q[16];
 #pragma unroll
         for (int i = 0; i < 16; i++) {
-            int dentro = rnd(g[p][i], ec - eg[p], kid, o + i) - rnd(y[p][i] * S, ec - (ey[p] + eS), kid, o + i);
+            // ec >= eg + 7 - 28 and ec >= ey + eS + 22 - 28: the 7-bit g moves up by at most 21, the 22-bit y S by at most 6
+            int dentro = desloca(g[p][i], ec - eg[p]) - desloca(y[p][i] * S, ec - (ey[p] + eS));
             const int sh2 = max(bitlen(dentro) - 18, 0);
             dentro = rnd_d(dentro, sh2);
             v[i] = dentro * inv;

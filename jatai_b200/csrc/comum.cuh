@@ -193,16 +193,17 @@ __device__ __forceinline__ int quant_geral(const int (&v)[NV], const int (&e)[NV
         if (v[i] != 0) topo = max(topo, e[i] + bitlen(v[i]));
     }
     topo = grupo_max<GL, ST>(topo, mask);
+    // E >= e[i] + bitlen(v[i]) - 7, so a left shift moves v[i] up to 7 bits at most: it cannot lose bits
     int E = topo - 7, over = 0;
 #pragma unroll
     for (int i = 0; i < NV; i++) {
-        q[i] = rnd(v[i], E - e[i], kid, idx0 + i);
+        q[i] = desloca(v[i], E - e[i]);
         over |= (q[i] > 127) | (q[i] < -127);
     }
     if (grupo_or<GL, ST>(over, mask)) {
         E += 1;
 #pragma unroll
-        for (int i = 0; i < NV; i++) q[i] = rnd(v[i], E - e[i], kid, idx0 + i);
+        for (int i = 0; i < NV; i++) q[i] = desloca(v[i], E - e[i]);
     }
     if (topo == SEM_TOPO || E < -126) {
 #pragma unroll
