@@ -2,7 +2,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload gemm|passo]
 
-Workloads (synthetic data with the shapes and value distributions BASELINE.json names: mantissas uniform in
+Workloads (synthetic data with the shapes and value distributions the reference benchmarks use: mantissas uniform in
 [-127,127], one exponent per 32-element K-block uniform in [-12,-4], seeded):
   passo  (default) one full training step of the 12-layer model (D=512, 8 heads, T=256, batch 8 = 2048 tokens per GPU),
          replayed from a CUDA graph; metric = tokens/s.
@@ -295,7 +295,7 @@ def braco_gemm(args):
 
 
 # ------------------------------------------------------------------------------------------------ training step
-PASSO = dict(V=256, D=512, H=8, FF=2048, L=12, Bt=8, T=256, k_lr=4)      # BASELINE config 4
+PASSO = dict(V=256, D=512, H=8, FF=2048, L=12, Bt=8, T=256, k_lr=4)      # benchmark configuration 4 of the reference
 
 
 def lote_tokens(seed, Bt, T, V):
@@ -524,7 +524,7 @@ def braco_passo(args):
 
 # ------------------------------------------------------------------------------------------------ fused op suite
 def braco_ops(args):
-    """BASELINE config 3: the bandwidth-bound ops at 16384 tokens x D=1024 (block 32); achieved HBM GB/s per op from
+    """Benchmark configuration 3: the bandwidth-bound ops at 16384 tokens x D=1024 (block 32); achieved HBM GB/s per op from
     the algorithmic bytes (inputs read once + outputs written once).  Inputs rotate over enough copies to exceed L2."""
     rank, local, mundo = dist_info()
     dev = torch.device("cuda", local if mundo > 1 else 0)

@@ -24,7 +24,7 @@ class Gen:
     def bloco(self, R, C, espalha=4, zera=0.0, e0=-10, mmax=127, faixa=None):
         blk = self.blk
         m = torch.randint(-mmax, mmax + 1, (R, C), generator=self.g, dtype=torch.int32).to(torch.int8)
-        if faixa is not None:          # explicit exponent range [lo, hi], as BASELINE config 1 states it
+        if faixa is not None:          # explicit exponent range [lo, hi], as benchmark configuration 1 states it
             E = torch.randint(faixa[0], faixa[1] + 1, (R, C // blk), generator=self.g).to(torch.int8)
         else:
             E = (e0 + torch.randint(-espalha, espalha + 1, (R, C // blk), generator=self.g)).to(torch.int8)
@@ -120,7 +120,7 @@ def _satura(t):
 
 
 def config1(blk=32):
-    """BASELINE config 1: one linear layer forward + both backward GEMMs, M=2048, K=N=512,
+    """Benchmark configuration 1: one linear layer forward + both backward GEMMs, M=2048, K=N=512,
     mantissas uniform in [-127,127], one exponent per K-block uniform in [-12,-4], seed 0."""
     G = Gen(0, blk)
     X = G.bloco(2048, 512, faixa=(-12, -4))

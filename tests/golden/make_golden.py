@@ -9,7 +9,7 @@ seeded inputs and its outputs are stored:
   * ops_b128.npz : the reference exactly as shipped (BLK = 128).
   * ops_b32.npz  : the same code with its block constant set to 32 (ops.BLK = 32 and the bound default
                    of ops.expande, the only two places the constant is captured).
-  * config1_b32.json : SHA-256 of every output of BASELINE config 1 (M=2048, K=N=512, block 32).
+  * config1_b32.json : SHA-256 of every output of benchmark configuration 1 (M=2048, K=N=512, block 32).
 Outputs larger than 32 KiB are stored as SHA-256 digests; input digests are stored for all cases so a
 change in the random generator is detected instead of silently comparing different inputs.
 """
@@ -80,7 +80,7 @@ def main():
         np.savez_compressed(os.path.join(AQUI, f"ops_b{blk}.npz"), **arrs)
         with open(os.path.join(AQUI, f"ops_b{blk}.json"), "w") as fh:
             json.dump(meta, fh, indent=1, sort_keys=True)
-    # BASELINE config 1 at block 32: Y = X.W^T, dX = dY.T(W)^T, dW = T(dY).T(X)^T raw (modelo.py:110-113)
+    # benchmark configuration 1 at block 32: Y = X.W^T, dX = dY.T(W)^T, dW = T(dY).T(X)^T raw (modelo.py:110-113)
     define_blk(O, 32)
     X, W, dY = casos.config1(32)
     r = O.OpsRef()

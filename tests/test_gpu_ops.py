@@ -111,7 +111,7 @@ def test_gemm_vias(amb, nome, blk, f, via):
 
 
 def test_config1(amb):
-    """BASELINE config 1: linear layer forward + both backward GEMMs at block 32, against the reference digests."""
+    """Benchmark configuration 1: linear layer forward + both backward GEMMs at block 32, against the reference digests."""
     import json
     ops, oc, reg = amb
     ops.define_blk(32)

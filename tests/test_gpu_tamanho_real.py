@@ -1,4 +1,4 @@
-"""Parity at the full sizes BASELINE.json names, where the CPU oracle is too slow to run whole:
+"""Parity at the full sizes of the reference benchmarks, where the CPU oracle is too slow to run whole:
   * config 2 GEMM shapes (K up to 16384): row slabs against the C restatement, all rows against a linearity-free
     property (two K halves with common row maxima add up to the full raw GEMM);
   * config 3/5 attention shape (T = 1024, head dim 64): one sequence against the int64 oracle evaluated on the GPU;
@@ -106,7 +106,7 @@ def test_atencao_T1024(amb):
 
 
 def test_config4_tres_passos_conferidos(amb):
-    """BASELINE config 4 (12 layers, D=512, 8 heads, T=256, batch 8): three training steps, every operation checked
+    """Benchmark configuration 4 (12 layers, D=512, 8 heads, T=256, batch 8): three training steps, every operation checked
     bit for bit against the int64 oracle running on the same GPU."""
     import conferido
     from jatai_b200 import modelo, ops, registro

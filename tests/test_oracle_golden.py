@@ -30,7 +30,7 @@ def test_spec_matches_reference(nome, blk, f):
 
 
 def test_config1_block32_digests():
-    """BASELINE config 1 (M=2048, K=N=512, block 32): Y, dX and raw dW of the oracle hash to the reference's."""
+    """Benchmark configuration 1 (M=2048, K=N=512, block 32): Y, dX and raw dW of the oracle hash to the reference's."""
     with open(os.path.join(gu.AQUI, "config1_b32.json")) as fh:
         rec = json.load(fh)
     X, W, dY = casos.config1(32)
