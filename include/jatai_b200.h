@@ -104,6 +104,11 @@ int jt_gemm_ext(const void* A, const void* EA, const void* B, const void* EB, vo
 /* R8[i] = max over the nb block exponents of row i of E (int8 [linhas, nb]): the RA / RB above. */
 int jt_max_linha(const void* E, void* R8, int linhas, int nb, int kid);
 
+/* jt_momento followed by jt_peso on the same tensors in one launch (the optimiser step of a weight is always this pair):
+ * same results as the two calls, one pass over the momentum.  Arguments as in jt_momento and jt_peso. */
+int jt_momento_peso(const void* gacc, const void* ge, void* Mm, void* ME, void* Wm, void* WE, void* Rm, void* RE, int k_lr, int ef,
+                    long long nblocos, int kid);
+
 /* jt_atencao_back for callers that may not allocate device memory (fixed memory budgets, code running where
  * cudaMalloc is forbidden): same arguments and results, but the workspace lives in a fixed 4 MiB device array
  * inside the library instead of a cudaMalloc'd buffer, and no allocating routine is called.  Refuses

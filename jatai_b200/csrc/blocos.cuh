@@ -235,6 +235,55 @@ __global__ void __launch_bounds__(256) k_peso(int8_t* __restrict__ Wm, int8_t* _
     if (lider) RE[w] = (int8_t)Er;
 }
 
+// momentum and weight step of the same 16 elements in one launch (the optimiser of a weight is always this pair):
+// k_momento followed by k_peso on the momentum just written, which stays in registers.
+template <int BLK>
+__global__ void __launch_bounds__(256) k_momento_peso(const int* __restrict__ gacc, const int16_t* __restrict__ ge, int8_t* __restrict__ Mm,
+                                                      int8_t* __restrict__ ME, int8_t* __restrict__ Wm, int8_t* __restrict__ WE,
+                                                      int8_t* __restrict__ Rm, int8_t* __restrict__ RE, int k_lr, int ef, long long n16, int kid) {
+    JT_FIO16
+    int mv[16], Em;
+    {
+        int mm[16], g[16], eg[16], v[16], ee[16];
+        le16(Mm + o, mm);
+        le16_i32(gacc + o, g);
+        le16_i16(ge + o, eg);
+        const int em = (int)ME[w] - 3;
+#pragma unroll
+        for (int i = 0; i < 16; i++) {
+            if (g[i] >= LIM || g[i] <= -LIM) reporta(E_ACUM, kid, o + i, g[i], eg[i]);
+            const int ec = max(em + 10, eg[i] + bitlen(g[i])) - 28;
+            v[i] = desloca(mm[i] * 7, ec - em) + desloca(g[i], ec - eg[i]);
+            ee[i] = ec;
+        }
+        Em = (int)(int8_t)quant_geral<16, BLK / 16>(v, ee, mv, kid, o);
+        if (ativo) grava16(Mm + o, mv);
+        if (lider) ME[w] = (int8_t)Em;
+    }
+    int wv[16], rv[16], alvo[16], q[16];
+    le16(Wm + o, wv);
+    if (ef) le16(Rm + o, rv);
+    else {
+#pragma unroll
+        for (int i = 0; i < 16; i++) rv[i] = 0;
+    }
+    const int ew = WE[w], em = Em - k_lr, er = ef ? (int)RE[w] : E_ZERO;
+    const int ec = max(max(ew + 7, em + 7), er + 7) - 27;
+#pragma unroll
+    for (int i = 0; i < 16; i++)
+        alvo[i] = desloca(wv[i], ec - ew) - desloca(mv[i], ec - em) + (ef ? desloca(rv[i], ec - er) : 0);
+    const int Ew = quant_uniforme<16, BLK / 16>(alvo, ec, q, kid, o);
+    if (ativo) grava16(Wm + o, q);
+    if (lider) WE[w] = (int8_t)Ew;
+    if (!ef) return;
+    int dif[16], r[16];
+#pragma unroll
+    for (int i = 0; i < 16; i++) dif[i] = alvo[i] - desloca(q[i], ec - Ew);
+    const int Er = quant_uniforme<16, BLK / 16>(dif, ec, r, kid, o);
+    if (ativo) grava16(Rm + o, r);
+    if (lider) RE[w] = (int8_t)Er;
+}
+
 // row gather of the embedding table; an out-of-range token zeroes the row and records E_ARG.  ops.py:143-145
 template <int BLK>
 __global__ void __launch_bounds__(256) k_embed(const int8_t* __restrict__ Wm, const int8_t* __restrict__ WE, const int* __restrict__ tok,

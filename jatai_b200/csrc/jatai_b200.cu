@@ -247,6 +247,15 @@ int jt_peso(void* Wm, void* WE, const void* Mm, const void* ME, void* Rm, void* 
 #undef ARGS
     return fim();
 }
+int jt_momento_peso(const void* gacc, const void* ge, void* Mm, void* ME, void* Wm, void* WE, void* Rm, void* RE, int k_lr, int ef,
+                    long long nblocos, int kid) {
+    const long long n16 = JT_N16;
+#define ARGS (const int*)gacc, (const int16_t*)ge, (int8_t*)Mm, (int8_t*)ME, (int8_t*)Wm, (int8_t*)WE, (int8_t*)Rm, (int8_t*)RE, k_lr, ef, n16, kid
+    if (g_blk == 32) k_momento_peso<32><<<nblocos16(n16), 256, 0, g_stream>>>(ARGS);
+    else k_momento_peso<128><<<nblocos16(n16), 256, 0, g_stream>>>(ARGS);
+#undef ARGS
+    return fim();
+}
 int jt_transpoe(const void* X, const void* EX, void* Y, void* EY, int R, int C, int kid) {
     if (R <= 0 || C <= 0 || R % 128 || C % 64 || C % g_blk) return (int)cudaErrorInvalidValue;
     if (g_blk == 32 && C % 256 == 0 && ((uintptr_t)EX & 3) == 0) {

@@ -143,8 +143,12 @@ class Modelo:
 
     def _otimiza(self, grads, k_lr):
         ops = self.ops
+        junto = getattr(ops, "momento_peso", None)        # one launch for the pair where the library has it
         for n, gr in grads.items():
             with self.reg.trecho(n):
+                if junto is not None:
+                    self.mom[n], self.p[n], self.res[n] = junto(gr, self.mom[n], self.p[n], self.res[n], k_lr, self.error_feedback)
+                    continue
                 self.mom[n] = ops.momento(gr, self.mom[n])
                 self.p[n], self.res[n] = ops.peso(self.p[n], self.mom[n], self.res[n], k_lr, self.error_feedback)
 

@@ -29,7 +29,7 @@ AQUI = os.path.dirname(os.path.abspath(__file__))
 BIBLIOTECA = os.path.join(AQUI, "libjatai_b200.so")
 
 _INT_FUNCS = ("jt_gemm", "jt_gemm_f", "jt_gemm_ext", "jt_max_linha", "jt_quant", "jt_soma", "jt_relu2", "jt_relu2_back",
-              "jt_momento", "jt_peso", "jt_transpoe", "jt_embed", "jt_um_quente", "jt_rms", "jt_rms_back", "jt_atencao",
+              "jt_momento", "jt_peso", "jt_momento_peso", "jt_transpoe", "jt_embed", "jt_um_quente", "jt_rms", "jt_rms_back", "jt_atencao",
               "jt_atencao_back", "jt_softmax_ce", "jt_erro_le", "jt_erro_limpa", "jt_sincroniza", "jt_para16", "jt_para8",
               "jt_soma16", "jt_res_estocastico", "jt_blk", "jt_blk_atual", "jt_gemm_via", "jt_gemm_tn", "jt_atencao_back_fixo")
 
@@ -302,6 +302,17 @@ class OpsCuda:
         self._lanca("momento", "jt_momento", (Gc[0], Gc[1], Mom[0], Mom[1]), (Mom[0].numel() // BLK,), dict(g=Gc[0], ge=Gc[1]),
                     tuple(Mom[0].shape), longos=(0,))
         return Mom
+
+    def momento_peso(self, Gc, Mom, W, R, k, ef):
+        """momento(Gc, Mom) followed by peso(W, Mom, R, k, ef) in one launch (an addition of this library; same results).
+        Returns (Mom, W, R), all updated in place."""
+        self.reg.confere_cru("grad", Gc)
+        for n, t in (("W", W), ("momento", Mom), ("residuo", R)):
+            self.reg.confere_bloco(n, t)
+        self.reg.exige(tuple(Gc[0].shape) == tuple(Mom[0].shape) == tuple(W[0].shape), "momento_peso: gradient, momentum and weight shapes differ")
+        self._lanca("momento_peso", "jt_momento_peso", (Gc[0], Gc[1], Mom[0], Mom[1], W[0], W[1], R[0], R[1]),
+                    (k, int(ef), W[0].numel() // BLK), dict(g=Gc[0], ge=Gc[1]), tuple(W[0].shape), longos=(2,))
+        return Mom, W, R
 
     def peso(self, W, Mom, R, k, ef):
         for n, t in (("W", W), ("momento", Mom), ("residuo", R)):

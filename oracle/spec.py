@@ -387,3 +387,10 @@ class Spec:
             return (w2, wE2), R
         back = torch.where(w2 == 0, torch.zeros_like(alvo), rnd(w2, ec - expande(wE2, blk)))
         return (w2, wE2), quant(alvo - back, ec, blk)
+
+    def momento_peso(self, Gc, Mom, W, R, k, ef):
+        """The optimiser step of one weight: momento then peso on its result (ops.py:273-290 composed; the CUDA library
+        offers the pair as one launch)."""
+        Mom2 = self.momento(Gc, Mom)
+        W2, R2 = self.peso(W, Mom2, R, k, ef)
+        return Mom2, W2, R2

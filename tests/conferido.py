@@ -26,7 +26,7 @@ class OpsConferido:
 
         def f(*args, **kw):
             cpu_args = [_cpu(a) for a in args]
-            if op in ("momento", "peso"):                       # in-place on the device: the oracle works on copies
+            if op in ("momento", "peso", "momento_peso"):                       # in-place on the device: the oracle works on copies
                 cpu_args = [tuple(t.clone() for t in a) if isinstance(a, tuple) else a for a in cpu_args]
             kw_r = {k: _cpu(v) for k, v in kw.items()}
             out_r = fr(*cpu_args, **kw_r)

@@ -311,3 +311,31 @@ def test_gemm_estagio_de_saida(amb, op, caso, tn):
         compara(f"{op} {caso} tn {tn}", outs, casos.roda(spec.Spec(32), op, args, {}))
     finally:
         oc.lib.jt_gemm_tn(0)
+
+
+@pytest.mark.parametrize("blk", [32, 128])
+@pytest.mark.parametrize("ef", [0, 1])
+def test_momento_peso_junto(amb, blk, ef):
+    """The fused optimiser launch gives the bits of momento followed by peso (and of the specification), including
+    zero blocks of momentum and residual and gradients of very different magnitudes."""
+    ops, oc, reg = amb
+    ops.define_blk(blk)
+    try:
+        reg.novo_passo(0)
+        G = casos.Gen(77 + blk + ef, blk)
+        R_, C_ = 256, 512
+        grad = G.cru(R_, C_, bits=26, e0=-35)
+        grad[0][::7] = 0
+        mom, w, res = G.bloco(R_, C_, espalha=6, zera=0.1, e0=-14), G.bloco(R_, C_, espalha=3, e0=-9), G.bloco(R_, C_, espalha=5, zera=0.2, e0=-17)
+        copia = lambda t: tuple(x.clone().cuda() for x in t)
+        g_d = para_gpu(grad)
+        m1, w1, r1 = copia(mom), copia(w), copia(res)
+        m1 = oc.momento(g_d, m1)
+        w1, r1 = oc.peso(w1, m1, r1, 4, ef)
+        m2, w2, r2 = oc.momento_peso(g_d, copia(mom), copia(w), copia(res), 4, ef)
+        torch.cuda.synchronize()
+        ref = spec.Spec(blk).momento_peso(grad, mom, w, res, 4, ef)
+        compara(f"momento_peso blk {blk} ef {ef} (vs separate launches)", casos.plano((m2, w2, r2)), casos.plano((m1, w1, r1)))
+        compara(f"momento_peso blk {blk} ef {ef} (vs specification)", casos.plano((m2, w2, r2)), casos.plano(ref))
+    finally:
+        ops.define_blk(32)

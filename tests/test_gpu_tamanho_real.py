@@ -116,7 +116,7 @@ def test_config4_tres_passos_conferidos(amb):
             fc, fr = getattr(self.c, op), getattr(self.r, op)
 
             def f(*args, **kw):
-                copia = [tuple(t.clone() for t in a) if isinstance(a, tuple) and op in ("momento", "peso") else a for a in args]
+                copia = [tuple(t.clone() for t in a) if isinstance(a, tuple) and op in ("momento", "peso", "momento_peso") else a for a in args]
                 out_r = fr(*copia, **kw)
                 out_c = fc(*args, **kw)
                 torch.cuda.synchronize()
