@@ -109,6 +109,11 @@ int jt_max_linha(const void* E, void* R8, int linhas, int nb, int kid);
 int jt_momento_peso(const void* gacc, const void* ge, void* Mm, void* ME, void* Wm, void* WE, void* Rm, void* RE, int k_lr, int ef,
                     long long nblocos, int kid);
 
+/* Two jt_transpoe calls on matrices with the same row count R ([R, C1] and [R, C2]) in one launch: the two operands of
+ * a weight-gradient GEMM.  Same results as the two calls. */
+int jt_transpoe2(const void* X1, const void* EX1, void* Y1, void* EY1, const void* X2, const void* EX2, void* Y2, void* EY2, int C1, int C2,
+                 int R, int kid);
+
 /* jt_atencao_back for callers that may not allocate device memory (fixed memory budgets, code running where
  * cudaMalloc is forbidden): same arguments and results, but the workspace lives in a fixed 4 MiB device array
  * inside the library instead of a cudaMalloc'd buffer, and no allocating routine is called.  Refuses

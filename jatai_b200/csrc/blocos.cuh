@@ -382,10 +382,9 @@ __device__ __noinline__ void transpoe32_lento(const uint32_t (*tile)[T32_PW], co
     *Edst = (int8_t)Eo;
 }
 
-template <int TR, int CPT = 4>
-__global__ void __launch_bounds__(8 * TR / CPT, 512 / (8 * TR / CPT)) k_transpoe32(const int8_t* __restrict__ X, const int8_t* __restrict__ EX,
-                                                                                   int8_t* __restrict__ Y, int8_t* __restrict__ EY, int R, int C,
-                                                                                   int kid) {
+template <int TR, int CPT>
+__device__ __forceinline__ void transpoe32_corpo(const int8_t* __restrict__ X, const int8_t* __restrict__ EX, int8_t* __restrict__ Y,
+                                                 int8_t* __restrict__ EY, int R, int C, int kid) {
     static_assert(CPT == 4 || CPT == 1, "a thread owns the 4 columns of a word or one of them");
     constexpr int TC = 256, PW = T32_PW, NT = 8 * TR / CPT;
     __shared__ uint32_t tile[TR][PW];
@@ -453,6 +452,23 @@ __global__ void __launch_bounds__(8 * TR / CPT, 512 / (8 * TR / CPT)) k_transpoe
         reinterpret_cast<uint4*>(dst)[1] = make_uint4(saida[4], saida[5], saida[6], saida[7]);
         *Edst = (int8_t)Eo;
     }
+}
+
+template <int TR, int CPT = 4>
+__global__ void __launch_bounds__(8 * TR / CPT, 512 / (8 * TR / CPT)) k_transpoe32(const int8_t* __restrict__ X, const int8_t* __restrict__ EX,
+                                                                                   int8_t* __restrict__ Y, int8_t* __restrict__ EY, int R, int C,
+                                                                                   int kid) {
+    transpoe32_corpo<TR, CPT>(X, EX, Y, EY, R, C, kid);
+}
+
+// Two transpositions of matrices with the same number of rows in one launch (the two operands of a weight-gradient
+// GEMM): blockIdx.z picks the matrix, the grid is as wide as the wider one.
+struct ArgsTransp { const int8_t* X; const int8_t* EX; int8_t* Y; int8_t* EY; int C; };
+template <int TR, int CPT = 4>
+__global__ void __launch_bounds__(8 * TR / CPT, 512 / (8 * TR / CPT)) k_transpoe32_par(ArgsTransp a0, ArgsTransp a1, int R, int kid) {
+    const ArgsTransp a = blockIdx.z ? a1 : a0;
+    if ((int)blockIdx.x * 256 >= a.C) return;
+    transpoe32_corpo<TR, CPT>(a.X, a.EX, a.Y, a.EY, R, a.C, kid);
 }
 
 // RMSNorm without gain, one warp per row, NP*512 >= D columns held in registers.  ops.py:153-165

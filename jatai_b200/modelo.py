@@ -66,6 +66,13 @@ class Modelo:
         if self.estatisticas:
             self.reg.estatistica(nome, t, zeros_normais)
 
+    def _transpoe_par(self, gy, x):
+        """Both operands of a weight-gradient GEMM transposed: one launch where the operator object offers the pair."""
+        par = getattr(self.ops, "transpoe2", None)
+        if par is not None and gy[0].shape[0] == x[0].shape[0]:
+            return par(gy, x)
+        return self.ops.transpoe(gy), self.ops.transpoe(x)
+
     def _grad_peso(self, nome, gy, x):
         """dW = gy^T . x as a raw tensor.  Both operands are transposed so that the reduced dimension (tokens)
         is the blocked one.  Data parallel: the GEMM is deferred - only the transposed operands and their row
@@ -73,7 +80,7 @@ class Modelo:
         backward, between the two collectives of the step (see `_gemms_adiados`)."""
         ops = self.ops
         if self._lado is None:
-            a, b = ops.transpoe(gy), ops.transpoe(x)
+            a, b = self._transpoe_par(gy, x)
             if self.redutor is None:
                 self._grads[nome] = ops.gemm(a, b, cru=True)
             else:
@@ -90,7 +97,7 @@ class Modelo:
             ops.lib.jt_stream(self._lado.cuda_stream)
             try:
                 self._otimiza_pendente()
-                a, b = ops.transpoe(gy), ops.transpoe(x)
+                a, b = self._transpoe_par(gy, x)
                 if self.redutor is None:
                     self._grads[nome] = ops.gemm(a, b, cru=True)
                     self._pendente = nome

@@ -29,7 +29,7 @@ AQUI = os.path.dirname(os.path.abspath(__file__))
 BIBLIOTECA = os.path.join(AQUI, "libjatai_b200.so")
 
 _INT_FUNCS = ("jt_gemm", "jt_gemm_f", "jt_gemm_ext", "jt_max_linha", "jt_quant", "jt_soma", "jt_relu2", "jt_relu2_back",
-              "jt_momento", "jt_peso", "jt_momento_peso", "jt_transpoe", "jt_embed", "jt_um_quente", "jt_rms", "jt_rms_back", "jt_atencao",
+              "jt_momento", "jt_peso", "jt_momento_peso", "jt_transpoe", "jt_transpoe2", "jt_embed", "jt_um_quente", "jt_rms", "jt_rms_back", "jt_atencao",
               "jt_atencao_back", "jt_softmax_ce", "jt_erro_le", "jt_erro_limpa", "jt_sincroniza", "jt_para16", "jt_para8",
               "jt_soma16", "jt_res_estocastico", "jt_blk", "jt_blk_atual", "jt_gemm_via", "jt_gemm_tn", "jt_atencao_back_fixo")
 
@@ -184,6 +184,21 @@ class OpsCuda:
         Y = self._bloco_vazio(C, R, m.device)
         self._lanca("transpoe", "jt_transpoe", (m, E, Y[0], Y[1]), (R, C), dict(X=m, EX=E), (C, R))
         return Y
+
+    def transpoe2(self, X1, X2):
+        """(transpoe(X1), transpoe(X2)) for two block tensors with the same number of rows, in one launch (an addition of
+        this library; the two operands of a weight-gradient GEMM)."""
+        self.reg.confere_bloco("X1", X1)
+        self.reg.confere_bloco("X2", X2)
+        (m1, E1), (m2, E2) = X1, X2
+        R, C1 = m1.shape
+        C2 = m2.shape[1]
+        self.reg.exige(m2.shape[0] == R, f"transpoe2: row counts differ ({R} and {m2.shape[0]})")
+        self.reg.exige(R % 128 == 0 and C1 % 64 == 0 and C2 % 64 == 0, f"transpoe2: rows {R} must be a multiple of 128 and columns {C1}, {C2} of 64")
+        Y1, Y2 = self._bloco_vazio(C1, R, m1.device), self._bloco_vazio(C2, R, m1.device)
+        self._lanca("transpoe2", "jt_transpoe2", (m1, E1, Y1[0], Y1[1], m2, E2, Y2[0], Y2[1]), (C1, C2, R), dict(X1=m1, EX1=E1, X2=m2, EX2=E2),
+                    (C1 + C2, R))
+        return Y1, Y2
 
     # ------------------------------------------------------------------ block elementwise
     def quant(self, Cc):

@@ -173,6 +173,10 @@ class Spec:
         """Row-maximum exponents of a block tensor: the RA / RB of gemm_acc (ops.py:98)."""
         return X[1].amax(1).to(torch.int8)
 
+    def transpoe2(self, X1, X2):
+        """Two transpositions (the CUDA library offers the pair as one launch)."""
+        return self.transpoe(X1), self.transpoe(X2)
+
     def transpoe(self, X):                                          # ops.py:121-123
         m, E = X
         return quant(m.to(I64).t().contiguous(), expande(E, self.blk).t().contiguous(), self.blk)

@@ -339,3 +339,24 @@ def test_momento_peso_junto(amb, blk, ef):
         compara(f"momento_peso blk {blk} ef {ef} (vs specification)", casos.plano((m2, w2, r2)), casos.plano(ref))
     finally:
         ops.define_blk(32)
+
+
+@pytest.mark.parametrize("blk,R,C1,C2", [(32, 256, 256, 512), (32, 2048, 512, 1536), (32, 2048, 256, 512), (32, 4096, 2048, 512),
+                                         (32, 8192, 2048, 2048), (32, 256, 192, 512), (128, 256, 256, 512)])
+def test_transpoe_par(amb, blk, R, C1, C2):
+    """The paired transposition launch gives the bits of two single launches and of the specification, for every tile
+    height it picks, unequal widths, a width that falls back to the generic kernel, and block 128."""
+    ops, oc, reg = amb
+    ops.define_blk(blk)
+    try:
+        reg.novo_passo(0)
+        G = casos.Gen(500 + R + C1 + C2, blk)
+        X1, X2 = G.bloco(R, C1, espalha=8, zera=0.1), G.bloco(R, C2, espalha=3, zera=0.05)
+        d1, d2 = para_gpu(X1), para_gpu(X2)
+        juntos = oc.transpoe2(d1, d2)
+        separados = (oc.transpoe(d1), oc.transpoe(d2))
+        torch.cuda.synchronize()
+        compara(f"transpoe2 {R}x({C1},{C2}) blk {blk} (vs single launches)", casos.plano(juntos), casos.plano(separados))
+        compara(f"transpoe2 {R}x({C1},{C2}) blk {blk} (vs specification)", casos.plano(juntos), casos.plano(spec.Spec(blk).transpoe2(X1, X2)))
+    finally:
+        ops.define_blk(32)
