@@ -109,6 +109,11 @@ int jt_max_linha(const void* E, void* R8, int linhas, int nb, int kid);
 int jt_momento_peso(const void* gacc, const void* ge, void* Mm, void* ME, void* Wm, void* WE, void* Rm, void* RE, int k_lr, int ef,
                     long long nblocos, int kid);
 
+/* jt_soma(x, jt_rms_back(g, y, cache)) in one launch: the residual add that always follows the RMSNorm backward.  x is a
+ * block tensor [M, D]; the other arguments as in jt_rms_back.  Same results as the two calls. */
+int jt_rms_back_soma(const void* gm, const void* gE, const void* ym, const void* yE, const void* cr, const void* cemax, const void* xm,
+                     const void* xE, void* om, void* oE, int M, int D, int log2D, int G, int GB, int kid);
+
 /* Two jt_transpoe calls on matrices with the same row count R ([R, C1] and [R, C2]) in one launch: the two operands of
  * a weight-gradient GEMM.  Same results as the two calls. */
 int jt_transpoe2(const void* X1, const void* EX1, void* Y1, void* EY1, const void* X2, const void* EX2, void* Y2, void* EY2, int C1, int C2,

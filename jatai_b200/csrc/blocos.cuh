@@ -55,6 +55,48 @@ __global__ void __launch_bounds__(256) k_quant(const int* __restrict__ acc, cons
     const long long nth_ = (long long)gridDim.x * blockDim.x;                             \
     const long long t0_ = (long long)blockIdx.x * blockDim.x + threadIdx.x;
 
+// One 16-element chunk of z = x + y (see k_soma below for the arithmetic); the GL lanes of a block call together.
+// Returns the block exponent, `pac` receives the 16 mantissas.
+template <int GL>
+__device__ __forceinline__ int soma16(const int (&xv)[16], int ex, const int (&yv)[16], int ey, uint4& pac, int kid, long long o) {
+    const bool x_maior = ex >= ey;
+    const int eH = x_maior ? ex : ey, d = x_maior ? ex - ey : ey - ex;
+    const int dl = min(d, 21), s2 = d - dl;                         // s2 > 0: the far operand is rounded first
+    int hi[16], lo[16], wv[16];
+#pragma unroll
+    for (int i = 0; i < 16; i++) { hi[i] = x_maior ? xv[i] : yv[i]; lo[i] = x_maior ? yv[i] : xv[i]; }
+    int mx = 0;
+#pragma unroll
+    for (int i = 0; i < 16; i++) {
+        wv[i] = (hi[i] << dl) + rnd_d(lo[i], s2);
+        mx = max(mx, wv[i] < 0 ? -wv[i] : wv[i]);
+    }
+    mx = grupo_max<GL>(mx);
+    int s = bitlen(mx) - 7;
+    if (desloca(mx, s) > 127) s += 1;
+    const int E = eH - dl + s;
+    pac = make_uint4(0, 0, 0, 0);
+    int Eo = E_ZERO;
+    if (mx != 0 && E >= -126) {
+        if (E > 126) reporta(E_EXP, kid, o, E, eH);
+        Eo = E;
+        int q[16];
+        if (s > 0) {
+            const int c = (1 << (s - 1)) - 1;
+#pragma unroll
+            for (int i = 0; i < 16; i++) q[i] = (wv[i] + c + ((wv[i] >> s) & 1)) >> s;
+        } else {
+#pragma unroll
+            for (int i = 0; i < 16; i++) q[i] = wv[i] << (-s);
+        }
+        pac.x = junta4(q[0], q[1], q[2], q[3]);
+        pac.y = junta4(q[4], q[5], q[6], q[7]);
+        pac.z = junta4(q[8], q[9], q[10], q[11]);
+        pac.w = junta4(q[12], q[13], q[14], q[15]);
+    }
+    return Eo;
+}
+
 // z = x + y.  ops.py:128-132: ec = max(xE, yE) - 21; v = rnd(x, ec - xE) + rnd(y, ec - yE); quant(v, ec).
 // With hi / lo = the operand of larger / smaller exponent and d their distance, v = 2^(21-dl) * w where dl = min(d, 21),
 // w = hi * 2^dl + lo' and lo' = lo (d <= 21) or rnd(lo, d - 21) (the specification rounds the far operand first).
@@ -80,41 +122,11 @@ __global__ void __launch_bounds__(256) k_soma(const int8_t* __restrict__ xm, con
 #pragma unroll
     for (int k = 0; k < U; k++) {
         JT_PEDACO(k)
-        const bool x_maior = ex[k] >= ey[k];
-        const int eH = x_maior ? ex[k] : ey[k], d = x_maior ? ex[k] - ey[k] : ey[k] - ex[k];
-        const int dl = min(d, 21), s2 = d - dl;                         // s2 > 0: the far operand is rounded first
-        int hi[16], lo[16], wv[16];
-        desempacota16(x_maior ? rx[k] : ry[k], hi);
-        desempacota16(x_maior ? ry[k] : rx[k], lo);
-        int mx = 0;
-#pragma unroll
-        for (int i = 0; i < 16; i++) {
-            wv[i] = (hi[i] << dl) + rnd_d(lo[i], s2);
-            mx = max(mx, wv[i] < 0 ? -wv[i] : wv[i]);
-        }
-        mx = grupo_max<GL>(mx);
-        int s = bitlen(mx) - 7;
-        if (desloca(mx, s) > 127) s += 1;
-        const int E = eH - dl + s;
-        uint4 pac = make_uint4(0, 0, 0, 0);
-        int Eo = E_ZERO;
-        if (mx != 0 && E >= -126) {
-            if (E > 126) reporta(E_EXP, kid, o, E, eH);
-            Eo = E;
-            int q[16];
-            if (s > 0) {
-                const int c = (1 << (s - 1)) - 1;
-#pragma unroll
-                for (int i = 0; i < 16; i++) q[i] = (wv[i] + c + ((wv[i] >> s) & 1)) >> s;
-            } else {
-#pragma unroll
-                for (int i = 0; i < 16; i++) q[i] = wv[i] << (-s);
-            }
-            pac.x = junta4(q[0], q[1], q[2], q[3]);
-            pac.y = junta4(q[4], q[5], q[6], q[7]);
-            pac.z = junta4(q[8], q[9], q[10], q[11]);
-            pac.w = junta4(q[12], q[13], q[14], q[15]);
-        }
+        int xv[16], yv[16];
+        desempacota16(rx[k], xv);
+        desempacota16(ry[k], yv);
+        uint4 pac;
+        const int Eo = soma16<GL>(xv, ex[k], yv, ey[k], pac, kid, o);
         if (ativo) *reinterpret_cast<uint4*>(zm + o) = pac;
         if (lider) zE[w] = (int8_t)Eo;
     }
@@ -534,10 +546,12 @@ __global__ void __launch_bounds__(256) k_rms(const int8_t* __restrict__ Xm, cons
 }
 
 // RMSNorm backward: dx = (g - y * mean(g y)) / rms with two shrink steps (15 and 18 bits).  ops.py:167-184
-template <int BLK, int NP>
-__global__ void __launch_bounds__(256) k_rms_back(const int8_t* __restrict__ gm, const int8_t* __restrict__ gE, const int8_t* __restrict__ ym,
-                                                  const int8_t* __restrict__ yE, const int* __restrict__ cr, const int* __restrict__ cemax,
-                                                  int8_t* __restrict__ om, int8_t* __restrict__ oE, int M, int D, int log2D, int G, int GB, int kid) {
+// SOMA: the result is added to the block tensor x (the residual gradient) before it is stored: soma(x, rms_back(...)).
+template <int BLK, int NP, bool SOMA>
+__device__ __forceinline__ void rms_back_corpo(const int8_t* __restrict__ gm, const int8_t* __restrict__ gE, const int8_t* __restrict__ ym,
+                                               const int8_t* __restrict__ yE, const int* __restrict__ cr, const int* __restrict__ cemax,
+                                               const int8_t* __restrict__ xm, const int8_t* __restrict__ xE, int8_t* __restrict__ om,
+                                               int8_t* __restrict__ oE, int M, int D, int log2D, int G, int GB, int kid) {
     constexpr int GL = BLK / 16;
     const int lane = threadIdx.x & 31;
     const long long lin_ = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
@@ -594,12 +608,33 @@ __global__ void __launch_bounds__(256) k_rms_back(const int8_t* __restrict__ gm,
             v[i] = dentro * inv;
             e[i] = ec + sh2 - k - (emax - G / 2);
         }
-        const int Eo = quant_geral<16, GL>(v, e, q, kid, o);
-        if (tem[p] && linha_ok) {
-            grava16(om + o, q);
-            if ((lane % GL) == 0) oE[lin * nb + c / BLK] = (int8_t)Eo;
-        }
+        int Eo = quant_geral<16, GL>(v, e, q, kid, o);
+        if (SOMA) {
+            int xv[16];
+            uint4 pac;
+            if (tem[p]) le16(xm + o, xv);
+            else {
+#pragma unroll
+                for (int i = 0; i < 16; i++) xv[i] = 0;
+            }
+            Eo = soma16<GL>(xv, tem[p] ? (int)xE[lin * nb + c / BLK] : E_ZERO, q, (int)(int8_t)Eo, pac, kid, o);
+            if (tem[p] && linha_ok) *reinterpret_cast<uint4*>(om + o) = pac;
+        } else if (tem[p] && linha_ok) grava16(om + o, q);
+        if (tem[p] && linha_ok && (lane % GL) == 0) oE[lin * nb + c / BLK] = (int8_t)Eo;
     }
+}
+template <int BLK, int NP>
+__global__ void __launch_bounds__(256) k_rms_back(const int8_t* __restrict__ gm, const int8_t* __restrict__ gE, const int8_t* __restrict__ ym,
+                                                  const int8_t* __restrict__ yE, const int* __restrict__ cr, const int* __restrict__ cemax,
+                                                  int8_t* __restrict__ om, int8_t* __restrict__ oE, int M, int D, int log2D, int G, int GB, int kid) {
+    rms_back_corpo<BLK, NP, false>(gm, gE, ym, yE, cr, cemax, nullptr, nullptr, om, oE, M, D, log2D, G, GB, kid);
+}
+template <int BLK, int NP>
+__global__ void __launch_bounds__(256) k_rms_back_soma(const int8_t* __restrict__ gm, const int8_t* __restrict__ gE, const int8_t* __restrict__ ym,
+                                                       const int8_t* __restrict__ yE, const int* __restrict__ cr, const int* __restrict__ cemax,
+                                                       const int8_t* __restrict__ xm, const int8_t* __restrict__ xE, int8_t* __restrict__ om,
+                                                       int8_t* __restrict__ oE, int M, int D, int log2D, int G, int GB, int kid) {
+    rms_back_corpo<BLK, NP, true>(gm, gE, ym, yE, cr, cemax, xm, xE, om, oE, M, D, log2D, G, GB, kid);
 }
 
 // integer softmax + cross-entropy gradient, one warp per row of raw logits.  ops.py:260-271

@@ -335,6 +335,13 @@ int jt_rms_back(const void* gm, const void* gE, const void* ym, const void* yE, 
              (int8_t*)om, (int8_t*)oE, M, D, log2D, G, GB, kid);
     return fim();
 }
+int jt_rms_back_soma(const void* gm, const void* gE, const void* ym, const void* yE, const void* cr, const void* cemax, const void* xm,
+                     const void* xE, void* om, void* oE, int M, int D, int log2D, int G, int GB, int kid) {
+    if (M <= 0 || D <= 0 || D % g_blk || D > 2048 || (1 << log2D) != D || !xm || !xE) return (int)cudaErrorInvalidValue;
+    JT_LINHA(k_rms_back_soma, D, (const int8_t*)gm, (const int8_t*)gE, (const int8_t*)ym, (const int8_t*)yE, (const int*)cr, (const int*)cemax,
+             (const int8_t*)xm, (const int8_t*)xE, (int8_t*)om, (int8_t*)oE, M, D, log2D, G, GB, kid);
+    return fim();
+}
 int jt_softmax_ce(const void* acc, const void* e, const void* alvo, void* gm, void* gE, void* d_alvo, void* soma, int M, int V, int log2M,
                   int kid) {
     if (M <= 0 || V <= 0 || V % g_blk || V > 2048) return (int)cudaErrorInvalidValue;

@@ -66,6 +66,13 @@ class Modelo:
         if self.estatisticas:
             self.reg.estatistica(nome, t, zeros_normais)
 
+    def _soma_rms_back(self, gx, gn, y, cache):
+        """gx + rms_back(gn, y, cache): one launch where the operator object offers the pair."""
+        junto = getattr(self.ops, "rms_back_soma", None)
+        if junto is not None:
+            return junto(gx, gn, y, cache)
+        return self.ops.soma(gx, self.ops.rms_back(gn, y, cache))
+
     def _transpoe_par(self, gy, x):
         """Both operands of a weight-gradient GEMM transposed: one launch where the operator object offers the pair."""
         par = getattr(self.ops, "transpoe2", None)
@@ -229,7 +236,7 @@ class Modelo:
                         gh = ops.gemm_relu2_back(gx, T_(p[f"Wd{l}"]), h)
                         self._grad_peso(f"Wup{l}", gh, n2)
                         gn = ops.gemm(gh, T_(p[f"Wup{l}"]))
-                        gx = ops.soma(gx, ops.rms_back(gn, n2, c2))
+                        gx = self._soma_rms_back(gx, gn, n2, c2)
                         self._st(f"c{l}.grad_mlp", gh, zeros_normais=True)
                     with reg.trecho("atencao"):
                         self._grad_peso(f"Wo{l}", gx, om)
@@ -237,7 +244,7 @@ class Modelo:
                         gq = ops.quant(ops.atencao_back(go, qkv, P, Bt, T, self.H))
                         self._grad_peso(f"Wqkv{l}", gq, n1)
                         gn = ops.gemm(gq, T_(p[f"Wqkv{l}"]))
-                        gx = ops.soma(gx, ops.rms_back(gn, n1, c1))
+                        gx = self._soma_rms_back(gx, gn, n1, c1)
                         self._st(f"c{l}.grad_qkv", gq); self._st(f"c{l}.grad_residuo", gx)
             with reg.trecho("embedding"):
                 self._grad_peso("emb", ops.um_quente(tok, self.V), gx)

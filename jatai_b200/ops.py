@@ -29,7 +29,7 @@ AQUI = os.path.dirname(os.path.abspath(__file__))
 BIBLIOTECA = os.path.join(AQUI, "libjatai_b200.so")
 
 _INT_FUNCS = ("jt_gemm", "jt_gemm_f", "jt_gemm_ext", "jt_max_linha", "jt_quant", "jt_soma", "jt_relu2", "jt_relu2_back",
-              "jt_momento", "jt_peso", "jt_momento_peso", "jt_transpoe", "jt_transpoe2", "jt_embed", "jt_um_quente", "jt_rms", "jt_rms_back", "jt_atencao",
+              "jt_momento", "jt_peso", "jt_momento_peso", "jt_transpoe", "jt_transpoe2", "jt_embed", "jt_um_quente", "jt_rms", "jt_rms_back", "jt_rms_back_soma", "jt_atencao",
               "jt_atencao_back", "jt_softmax_ce", "jt_erro_le", "jt_erro_limpa", "jt_sincroniza", "jt_para16", "jt_para8",
               "jt_soma16", "jt_res_estocastico", "jt_blk", "jt_blk_atual", "jt_gemm_via", "jt_gemm_tn", "jt_atencao_back_fixo")
 
@@ -268,6 +268,19 @@ class OpsCuda:
         O = self._bloco_vazio(M, D, g.device)
         self._lanca("rms_back", "jt_rms_back", (g, gE, y, yE, cache[0], cache[1], O[0], O[1]), (M, D, int(math.log2(D)), G, GB),
                     dict(g=g, gE=gE, y=y, yE=yE, r=cache[0], emax=cache[1]), (M, D))
+        return O
+
+    def rms_back_soma(self, X, Gg, Y, cache):
+        """soma(X, rms_back(Gg, Y, cache)) in one launch (an addition of this library; same results)."""
+        for n, t in (("x", X), ("g", Gg), ("y", Y)):
+            self.reg.confere_bloco(n, t)
+        (g, gE), (y, yE) = Gg, Y
+        M, D = g.shape
+        self.reg.exige(tuple(X[0].shape) == (M, D), f"rms_back_soma: x has shape {tuple(X[0].shape)}, expected {(M, D)}")
+        G, GB = g_rms(D)
+        O = self._bloco_vazio(M, D, g.device)
+        self._lanca("rms_back_soma", "jt_rms_back_soma", (g, gE, y, yE, cache[0], cache[1], X[0], X[1], O[0], O[1]),
+                    (M, D, int(math.log2(D)), G, GB), dict(g=g, gE=gE, y=y, yE=yE, r=cache[0], emax=cache[1], x=X[0], xE=X[1]), (M, D))
         return O
 
     # ------------------------------------------------------------------ attention

@@ -173,6 +173,10 @@ class Spec:
         """Row-maximum exponents of a block tensor: the RA / RB of gemm_acc (ops.py:98)."""
         return X[1].amax(1).to(torch.int8)
 
+    def rms_back_soma(self, X, Gg, Y, cache):
+        """soma(X, rms_back(Gg, Y, cache)) (the CUDA library offers the pair as one launch)."""
+        return self.soma(X, self.rms_back(Gg, Y, cache))
+
     def transpoe2(self, X1, X2):
         """Two transpositions (the CUDA library offers the pair as one launch)."""
         return self.transpoe(X1), self.transpoe(X2)

@@ -360,3 +360,25 @@ def test_transpoe_par(amb, blk, R, C1, C2):
         compara(f"transpoe2 {R}x({C1},{C2}) blk {blk} (vs specification)", casos.plano(juntos), casos.plano(spec.Spec(blk).transpoe2(X1, X2)))
     finally:
         ops.define_blk(32)
+
+
+@pytest.mark.parametrize("blk,M,D", [(32, 256, 512), (32, 128, 1024), (32, 64, 2048), (32, 40, 256), (128, 256, 512)])
+def test_rms_back_soma_junto(amb, blk, M, D):
+    """The fused RMSNorm-backward + residual-add launch gives the bits of the two launches and of the specification
+    (rows that do not fill the last CTA, every row width the kernel is instantiated for, zero blocks in the residual)."""
+    ops, oc, reg = amb
+    ops.define_blk(blk)
+    try:
+        reg.novo_passo(0)
+        G = casos.Gen(900 + M + D, blk)
+        x = G.bloco(M, D, espalha=5, zera=0.1, e0=-12)
+        y, cache = spec.Spec(blk).rms(x)
+        g, res = G.bloco(M, D, espalha=4, e0=-20), G.bloco(M, D, espalha=6, zera=0.15, e0=-19)
+        dg, dy, dc, dr = para_gpu(g), para_gpu(y), tuple(t.cuda() for t in cache), para_gpu(res)
+        junto = oc.rms_back_soma(dr, dg, dy, dc)
+        separado = oc.soma(dr, oc.rms_back(dg, dy, dc))
+        torch.cuda.synchronize()
+        compara(f"rms_back_soma {M}x{D} blk {blk} (vs two launches)", casos.plano(junto), casos.plano(separado))
+        compara(f"rms_back_soma {M}x{D} blk {blk} (vs specification)", casos.plano(junto), casos.plano(spec.Spec(blk).rms_back_soma(res, g, y, cache)))
+    finally:
+        ops.define_blk(32)
