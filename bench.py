@@ -295,6 +295,7 @@ def braco_gemm(args):
 
 
 # ------------------------------------------------------------------------------------------------ training step
+TRAFEGO_GEMMS_PASSO = 601.5e6        # bytes per step, measured with ncu on this workload (see roofline.traffic_note)
 PASSO = dict(V=256, D=512, H=8, FF=2048, L=12, Bt=8, T=256, k_lr=4)      # benchmark configuration 4 of the reference
 
 
@@ -503,7 +504,9 @@ def braco_passo(args):
                    "l2": "weights + momentum + residual + activations of a step exceed L2 (about 0.6 GB touched per step)",
                    "init": "seeded random weights (reference recipe), uniform random byte tokens"},
         "loss_last": perda_f, "launches_per_step": lancamentos,
-        "roofline": {"bound": "tensor", "achieved": ach, "peak": pico_i8, "unit": "TOPS", "frac": (ach / pico_i8) if ach else None, "traffic": None,
+        "roofline": {"bound": "tensor", "achieved": ach, "peak": pico_i8, "unit": "TOPS", "frac": (ach / pico_i8) if ach else None,
+                     "traffic": TRAFEGO_GEMMS_PASSO if (mundo == 1 and args.via is None and BLK == 32) else None,
+                     "traffic_note": "DRAM bytes read + written by the step's 148 GEMM launches, one ncu pass (cold L2 per launch; the outputs stay in L2): profiles/k_gemm_tc_b32.md",
                      "kernel": f"all {n_gemms} block GEMMs of one step (k_gemm_tc), issued back to back from one CUDA graph with the step's own operands",
                      "peak_source": f"2 x cuBLAS bf16 sustained ({pk['origem']})", "gemm_ms_per_step": gemm_ms},
         "ms_per_op_eager": perfil["ms_per_op"], "clocks": clocks,
