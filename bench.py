@@ -1,23 +1,32 @@
 """Benchmark of the integer training hot path on B200.  Prints ONE JSON line (rank 0).
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload gemm|passo]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload passo|gemm|ops] [--config c4|c5|compat]
 
-Workloads (synthetic data with the shapes and value distributions the reference benchmarks use: mantissas uniform in
-[-127,127], one exponent per 32-element K-block uniform in [-12,-4], seeded):
-  passo  (default) one full training step of the 12-layer model (D=512, 8 heads, T=256, batch 8 = 2048 tokens per GPU),
-         replayed from a CUDA graph; metric = tokens/s.
-  gemm   block-32 INT8 GEMM trio of one linear layer at (M,K,N) = (16384,4096,4096):
-         Y = X.W^T, dX = dY.T(W)^T, dW = T(dY).T(X)^T raw.  A step = the three GEMMs; metric = TOPS (2.M.N.K each).
-  ops    the bandwidth-bound fused ops at 16384 tokens x D=1024: achieved HBM GB/s per op (single GPU).
-With N > 1 (torchrun, one rank per GPU): gemm runs independent replicas (the path has no exchange step);
-passo is data parallel with the bit-exact gradient reduction of jatai_b200.paralelo.
+Synthetic data with the shapes and value distributions the reference benchmarks use (mantissas uniform in [-127,127],
+one exponent per 32-element block uniform in [-12,-4], seeded; uniform random byte tokens) stands in for the corpus.
 
-`--impl reference` times the CPU restatement of the reference specification (oracle/, all host threads) on a
-bounded sample of the same workload; it is the only mode in which this file executes anything under oracle/
-apart from the `cpu_baseline` leg of the default mode.
+Workloads:
+  passo  (default) one full training step replayed from a CUDA graph; metric = tokens/s.  The headline configuration is
+         c4 = 12 layers, D=512, 8 heads, T=256, batch 8 = 2048 tokens per GPU (benchmark configuration 4).  The line also
+         carries, under "extra", short timed legs of the other benchmark configurations:
+           config5  24 layers, D=1024, 16 heads, T=1024, 16 sequences = 16384 tokens per GPU (data parallel when N > 1)
+           config2  block-32 GEMM sweep (N = 1 only): three shapes x {Y, dX, dW raw}, GEMM alone and GEMM + its transposes
+           config3  the bandwidth-bound fused ops at 16384 tokens x D=1024 (N = 1 only): achieved HBM GB/s per op
+           compat   the reference's own model size (D=256, 64 heads of 4, T=128, block 128; N = 1 only)
+         `--config c5` / `--config compat` make that configuration the headline instead; `--sem-extras` drops the legs.
+  gemm   the GEMM trio of one linear layer at (M,K,N) = (16384,4096,4096); metric = TOPS (2.M.N.K each).
+  ops    configuration 3 alone.
+With N > 1 (torchrun, one rank per GPU) passo is data parallel with the bit-exact gradient reduction of
+jatai_b200.paralelo (weak scaling); after the timed region the ranks compare a SHA-256 of weights, momentum and residual.
+
+`--impl reference` times the CPU restatement of the reference specification (oracle/, all host threads) on a bounded
+sample of the same workload and, when the reference's own CUDA library was compiled (oracle/_ref), that library on the
+GPU in the one configuration it supports (compat).  Apart from the `cpu_baseline` leg of the default mode this is the
+only mode in which this file executes anything under oracle/.
 """
 import argparse
 import ctypes
+import hashlib
 import json
 import os
 import subprocess
@@ -33,6 +42,18 @@ sys.path.insert(0, RAIZ)
 
 FORMA = dict(M=16384, K=4096, N=4096)
 BLK = 32
+CONFIGS = {
+    # benchmark configuration 4: the headline
+    "c4": dict(V=256, D=512, H=8, FF=2048, L=12, Bt=8, T=256, k_lr=4, blk=32),
+    # benchmark configuration 5: 16384 tokens per GPU
+    "c5": dict(V=256, D=1024, H=16, FF=4096, L=24, Bt=16, T=1024, k_lr=4, blk=32),
+    # the reference library's own size (jatai_cuda/treino_cuda.py:31-33), 2048 tokens per step, block 128
+    "compat": dict(V=256, D=256, H=64, FF=1024, L=12, Bt=16, T=128, k_lr=4, blk=128),
+}
+SWEEP = [(16384, 4096, 4096), (16384, 4096, 16384), (16384, 16384, 4096)]        # benchmark configuration 2
+# DRAM bytes read + written per launch of the tensor-core GEMM, from one ncu capture (1 launch, --clock-control none,
+# cold L2) of the 4096 x 4096 x 4096 block GEMM; other shapes scale by their algorithmic bytes (traffic grows with them)
+TRAFEGO_NCU = dict(bytes=36.9e6, forma=(4096, 4096, 4096), fonte="ncu dram__bytes_read.sum + dram__bytes_write.sum, k_gemm_tc 4096x4096x4096, 1 launch")
 
 
 # ------------------------------------------------------------------------------------------------ helpers
@@ -41,9 +62,13 @@ def picos():
     try:
         with open(os.path.join(RAIZ, "MEASURED_PEAKS.json")) as fh:
             p = json.load(fh)
-        return dict(hbm_gbs=p["hbm_gbs"], bf16=p["bf16_tflops"], bf16_sust=p.get("bf16_tflops_sustained"), origem="measured")
+        return dict(hbm_gbs=p["hbm_gbs"], bf16=p["bf16_tflops"], bf16_sust=p.get("bf16_tflops_sustained") or p["bf16_tflops"], origem="measured")
     except Exception:
         return dict(hbm_gbs=6650.0, bf16=1590.0, bf16_sust=1400.0, origem="fallback")
+
+
+def nome_passo(c):
+    return f"passo_{c['L']}L_D{c['D']}_H{c['H']}_T{c['T']}_Bt{c['Bt']}_b{c['blk']}"
 
 
 class Relogios:
@@ -92,20 +117,17 @@ class Relogios:
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": sorted(razoes), "samples": len(sm)}
 
 
-def gera_bloco(R, C, seed, dev, pinned=False):
+def gera_bloco(R, C, seed, dev, pinned=False, blk=BLK):
     g = torch.Generator(device="cpu").manual_seed(seed)
     m = torch.randint(-127, 128, (R, C), generator=g, dtype=torch.int32).to(torch.int8)
-    E = torch.randint(-12, -3, (R, C // BLK), generator=g).to(torch.int8)
+    E = torch.randint(-12, -3, (R, C // blk), generator=g).to(torch.int8)
     if pinned:
         return m.pin_memory(), E.pin_memory()
     return m.to(dev), E.to(dev)
 
 
 def dist_info():
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    mundo = int(os.environ.get("WORLD_SIZE", "1"))
-    return rank, local, mundo
+    return int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
 
 
 def barreira(mundo):
@@ -122,7 +144,43 @@ def max_ranks(ms, mundo, dev):
     return float(t.item())
 
 
-# ------------------------------------------------------------------------------------------------ CPU arm
+def ev():
+    return torch.cuda.Event(enable_timing=True)
+
+
+def inicia_gpu():
+    rank, local, mundo = dist_info()
+    if mundo > 1:
+        torch.cuda.set_device(local)
+        if not torch.distributed.is_initialized():
+            torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", local))
+    dev = torch.device("cuda", local if mundo > 1 else 0)
+    torch.cuda.set_device(dev)
+    return rank, mundo, dev
+
+
+def lanca_ops(blk, rotulo, biblioteca=None):
+    from jatai_b200 import ops, registro
+    ops.define_blk(blk)
+    reg = registro.Registro(tempfile.mkdtemp(), rotulo, eco=False, salvar=False)
+    oc = ops.OpsCuda(reg, biblioteca=biblioteca)
+    reg.novo_passo(0)
+    return ops, oc, reg
+
+
+def sem_erros(reg, onde):
+    n = reg.lib.jt_erro_le((ctypes.c_longlong * 6)())
+    assert n == 0, f"{onde}: device error record has {n} events"
+
+
+def n_threads():
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+# ------------------------------------------------------------------------------------------------ CPU legs (the oracle, timed)
 def oracle_gemm_lib():
     so = os.path.join(RAIZ, "oracle", "liboracle_gemm.so")
     if not os.path.exists(so):
@@ -149,9 +207,9 @@ def cpu_gemm_amostra(linhas):
     return 2.0 * linhas * N * K / dt / 1e12, dt, lib.oracle_threads()
 
 
-def braco_referencia(args):
-    """`--impl reference`: the CPU restatement of the reference specification, all host threads, bounded sample."""
-    rank, _, mundo = dist_info()
+def braco_referencia_gemm(args):
+    """`--impl reference --workload gemm`: the C restatement of the GEMM specification, all host threads, bounded sample."""
+    rank, _, _ = dist_info()
     if rank != 0:
         return
     linhas = 1024
@@ -171,29 +229,104 @@ def braco_referencia(args):
         "e2e": {"value": tops, "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}))
 
 
-# ------------------------------------------------------------------------------------------------ our arm
+def lote_tokens(seed, Bt, T, V):
+    """Uniform random byte tokens; inputs and targets shifted by one (the reference's batch recipe, treino.py:41-44)."""
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randint(0, V, (Bt, T + 1), generator=g)
+    return x[:, :-1].contiguous(), x[:, 1:].contiguous()
+
+
+def cpu_passo_amostra(c, Bt_am=2):
+    """Times the int64 restatement of the specification on reduced models (same D, heads, T, FF; 1 and 2 layers, Bt_am
+    sequences) with every host thread.  The difference of the two timings is the cost of one layer, the rest is the part
+    that does not grow with depth (embedding, logits, loss, their gradients and updates); the full step is estimated as
+    rest + L x layer, for Bt_am sequences.  Returns (tokens/s, seconds spent, threads, description)."""
+    from jatai_b200 import modelo, ops, registro
+    from oracle import spec
+    th = n_threads()
+    torch.set_num_threads(th)
+    antes = ops.BLK
+    ops.BLK = c["blk"]
+    tempos = {}
+    try:
+        tok, alvo = lote_tokens(1, Bt_am, c["T"], c["V"])
+        for L_am in (1, 2):
+            reg = registro.Registro(tempfile.mkdtemp(), "cpu", eco=False)
+            m = modelo.Modelo(c["V"], c["D"], c["H"], c["FF"], L_am, 0, "cpu", spec.Spec(c["blk"]), reg)
+            t0 = time.perf_counter()
+            m.passo(tok, alvo, k_lr=c["k_lr"])
+            tempos[L_am] = time.perf_counter() - t0
+    finally:
+        ops.BLK = antes
+    camada = max(tempos[2] - tempos[1], 1e-9)
+    resto = max(tempos[1] - camada, 0.0)
+    total = resto + c["L"] * camada
+    tps = Bt_am * c["T"] / total
+    txt = (f"int64 torch restatement of the spec on {th} threads: {Bt_am} of {c['Bt']} sequences of T={c['T']}, models of 1 and 2 layers "
+           f"({tempos[1]:.1f} s, {tempos[2]:.1f} s) -> layer {camada:.2f} s, depth-independent part {resto:.2f} s, step = rest + {c['L']} x layer; "
+           f"same_config: false (sampled sequences and layers)")
+    return tps, tempos[1] + tempos[2], th, txt
+
+
+def gpu_compat_referencia(steps):
+    """The reference's own CUDA library (dp4a kernels, compiled for sm_100a into oracle/_ref by the oracle's recipe) on the one
+    configuration it supports, through the same launcher and model code: tokens/s of the graph-replayed step, or None."""
+    so = os.path.join(RAIZ, "oracle", "_ref", "libjatai_ref.so")
+    if not (os.path.exists(so) and torch.cuda.is_available()):
+        return None
+    torch.cuda.set_device(0)
+    r = mede_passo(CONFIGS["compat"], 0, 1, torch.device("cuda", 0), steps=max(steps, 5), warmup=3, biblioteca=so, perfil=False, e2e=False)
+    return {"tokens_per_s": r["tps"], "ms_per_step": r["ms"], "launches_per_step": r["lancamentos"], "library": "oracle/_ref/libjatai_ref.so (reference jatai_cuda.cu, sm_100a)",
+            "config": nome_passo(CONFIGS["compat"])}
+
+
+def braco_referencia_passo(args):
+    rank, _, _ = dist_info()
+    if rank != 0:
+        return
+    c = CONFIGS[args.config]
+    vals = []
+    w = min(args.warmup, 1)
+    for i in range(w + min(args.steps, 2)):
+        tps, dt, th, txt = cpu_passo_amostra(c)
+        if i >= w:
+            vals.append((tps, dt))
+    tps = sum(v for v, _ in vals) / len(vals)
+    saida = {
+        "impl": "reference", "metric": "train_tokens_per_s", "value": tps, "unit": "tokens/s", "n_gpus": args.gpus, "steps": len(vals),
+        "warmup": w, "ms_per_step": 1e3 * c["Bt"] * c["T"] / tps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "int8+int32", "data": "synthetic", "same_config": False,
+        "config": {"workload": nome_passo(c), "sample": txt},
+        "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": th, "kind": "port", "sample": txt},
+        "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
+    try:
+        comp = gpu_compat_referencia(args.steps)
+        if comp is not None:
+            saida["extra"] = {"compat_reference_kernels": comp}
+    except Exception as e:
+        saida["extra"] = {"compat_reference_kernels": {"failed": f"{type(e).__name__}: {e}"}}
+    print(json.dumps(saida))
+
+
+# ------------------------------------------------------------------------------------------------ GEMM workload
+def bytes_gemm(M, K, N, blk, cru):
+    """Algorithmic bytes of one block GEMM: operands and exponents in, output out."""
+    b1 = 1 + 1.0 / blk
+    return (M * K + N * K) * b1 + M * N * (6 if cru else b1)
+
+
 def braco_gemm(args):
-    rank, local, mundo = dist_info()
-    if mundo > 1:
-        torch.cuda.set_device(local)
-        torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", local))
-    dev = torch.device("cuda", local if mundo > 1 else 0)
-    torch.cuda.set_device(dev)
-    from jatai_b200 import ops, registro
-    ops.define_blk(BLK)
-    reg = registro.Registro(tempfile.mkdtemp(), f"bench{rank}", eco=False, salvar=False)
-    oc = ops.OpsCuda(reg)
+    rank, mundo, dev = inicia_gpu()
+    ops, oc, reg = lanca_ops(BLK, f"bench{rank}")
     oc.lib.jt_stream(ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
     if args.via is not None:
         assert oc.lib.jt_gemm_via(args.via) == 0
     M, K, N = FORMA["M"], FORMA["K"], FORMA["N"]
-    reg.novo_passo(0)
     # operands of the three GEMMs, resident; 288 MB of mantissas per step > L2 (126 MB), so no flush is needed
     X, W, dY = gera_bloco(M, K, 1 + rank, dev), gera_bloco(N, K, 2, dev), gera_bloco(M, N, 3 + rank, dev)
     Wt, dYt, Xt = oc.transpoe(W), oc.transpoe(dY), oc.transpoe(X)
     torch.cuda.synchronize()
     ops_por_gemm = 2.0 * M * N * K
-    ev = lambda: torch.cuda.Event(enable_timing=True)
 
     def passo(tempos=None):
         reg.lancamentos = []
@@ -225,8 +358,7 @@ def braco_gemm(args):
     ms_passo = ms_total / args.steps
     tops = mundo * 3 * ops_por_gemm / (ms_passo * 1e-3) / 1e12
     por_gemm = [sum(t[i].elapsed_time(t[i + 1]) for t in tempos) / len(tempos) for i in range(3)]
-    n = reg.lib.jt_erro_le((ctypes.c_longlong * 6)())
-    assert n == 0, f"device error record has {n} events"
+    sem_erros(reg, "gemm")
 
     # end to end through the operator API with HOST buffers: H2D of the six operands, three GEMMs, D2H of the results
     Xh, Wh, dYh = gera_bloco(M, K, 1 + rank, dev, True), gera_bloco(N, K, 2, dev, True), gera_bloco(M, N, 3 + rank, dev, True)
@@ -268,6 +400,7 @@ def braco_gemm(args):
     pk = picos()
     pico_i8 = 2.0 * pk["bf16"]
     ach = ops_por_gemm / (por_gemm[0] * 1e-3) / 1e12
+    alg = bytes_gemm(M, K, N, BLK, False)
     saida = {
         "metric": "int8_b32_gemm_tops", "value": tops, "unit": "TOPS", "n_gpus": mundo, "steps": args.steps, "warmup": max(args.warmup, 3),
         "ms_per_step": ms_passo, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8+int32",
@@ -276,7 +409,10 @@ def braco_gemm(args):
                    "l2": "inputs larger than L2 (288 MB of operands per step)", "parallelism": f"replicas x{mundo}",
                    "via": args.via if args.via is not None else 0},
         "ms_per_gemm": {"fwd": por_gemm[0], "dX": por_gemm[1], "dW_raw": por_gemm[2]},
-        "roofline": {"bound": "tensor", "achieved": ach, "peak": pico_i8, "unit": "TOPS", "frac": ach / pico_i8, "traffic": None,
+        "roofline": {"bound": "tensor", "achieved": ach, "peak": pico_i8, "unit": "TOPS", "frac": ach / pico_i8,
+                     "frac_of_2x_bf16_sustained": ach / (2.0 * pk["bf16_sust"]),
+                     "traffic": TRAFEGO_NCU["bytes"] * alg / bytes_gemm(*TRAFEGO_NCU["forma"], BLK, False), "traffic_source": TRAFEGO_NCU["fonte"] + ", scaled by algorithmic bytes",
+                     "algorithmic_bytes": alg,
                      "kernel": "k_gemm_tc<32,0> forward GEMM", "peak_source": f"2 x cuBLAS bf16 burst ({pk['origem']}): kind::i8 issues at twice the bf16 rate",
                      "alu_bound_note": "every 32-wide K slice is drained from tensor memory and rounded on the CUDA cores: M*N*K/32 element-steps"},
         "clocks": clocks,
@@ -294,75 +430,64 @@ def braco_gemm(args):
     print(json.dumps(saida))
 
 
+def mede_sweep(oc, reg, dev, reps=3):
+    """Benchmark configuration 2: for each (M,K,N) the three GEMMs of a linear layer in the C[rows,cols] = A[rows,red] . B[cols,red]^T
+    convention - Y[M,N] (red K), dX[M,K] (red N, B = T(W)), dW raw [N,K] (red M, A = T(dY), B = T(X)) - timed alone and with the
+    transpositions they need (the method of the reference's bench_formas.py:56).  2.M.N.K operations each."""
+    pk = picos()
+    pico = 2.0 * pk["bf16"]
+    saida = {}
+
+    def cronometra(f):
+        f()
+        torch.cuda.synchronize()
+        a, b = ev(), ev()
+        a.record()
+        for _ in range(reps):
+            reg.lancamentos = []
+            f()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / reps
+
+    for (M, K, N) in SWEEP:
+        X, W, dY = gera_bloco(M, K, 21, dev), gera_bloco(N, K, 22, dev), gera_bloco(M, N, 23, dev)
+        Wt = oc.transpoe(W)
+        dYt, Xt = oc.transpoe2(dY, X)
+        ops_ = 2.0 * M * N * K
+        linhas = {}
+        for nome, so, com in (("Y", lambda: oc.gemm(X, W), None),
+                              ("dX", lambda: oc.gemm(dY, Wt), lambda: oc.gemm(dY, oc.transpoe(W))),
+                              ("dW_raw", lambda: oc.gemm(dYt, Xt, cru=True), lambda: oc.gemm(*oc.transpoe2(dY, X), cru=True))):
+            ms = cronometra(so)
+            tops = ops_ / (ms * 1e-3) / 1e12
+            linhas[nome] = {"ms": round(ms, 4), "TOPS": round(tops, 1), "frac_of_2x_bf16_burst": round(tops / pico, 4)}
+            if com is not None:
+                ms2 = cronometra(com)
+                linhas[nome].update({"ms_with_transposes": round(ms2, 4), "TOPS_with_transposes": round(ops_ / (ms2 * 1e-3) / 1e12, 1)})
+        saida[f"{M}x{K}x{N}"] = linhas
+        del X, W, dY, Wt, dYt, Xt
+        torch.cuda.empty_cache()
+    sem_erros(reg, "config2")
+    return {"shapes_MKN": saida, "peak_TOPS": pico, "peak_source": f"2 x cuBLAS bf16 burst ({pk['origem']})", "reps": reps,
+            "l2": "operands of every GEMM exceed L2", "ops": "2*M*N*K per GEMM"}
+
+
 # ------------------------------------------------------------------------------------------------ training step
-TRAFEGO_GEMMS_PASSO = 601.5e6        # bytes per step, measured with ncu on this workload (see roofline.traffic_note)
-PASSO = dict(V=256, D=512, H=8, FF=2048, L=12, Bt=8, T=256, k_lr=4)      # benchmark configuration 4 of the reference
-
-
-def lote_tokens(seed, Bt, T, V):
-    """Uniform random byte tokens; inputs and targets shifted by one (the reference's batch recipe, treino.py:41-44)."""
-    g = torch.Generator().manual_seed(seed)
-    x = torch.randint(0, V, (Bt, T + 1), generator=g)
-    return x[:, :-1].contiguous(), x[:, 1:].contiguous()
-
-
-def cpu_passo_amostra(L_am=2, Bt_am=2):
-    """Times the int64 restatement of the specification on a reduced model (same D, heads, T, FF; fewer layers and
-    sequences), scaled to the full step by layer and sequence count.  Returns (tokens/s scaled, seconds, threads, text)."""
-    from jatai_b200 import modelo, ops, registro
-    from oracle import spec
-    c = PASSO
-    antes = ops.BLK
-    ops.BLK = BLK
-    try:
-        reg = registro.Registro(tempfile.mkdtemp(), "cpu", eco=False)
-        m = modelo.Modelo(c["V"], c["D"], c["H"], c["FF"], L_am, 0, "cpu", spec.Spec(BLK), reg)
-        tok, alvo = lote_tokens(1, Bt_am, c["T"], c["V"])
-        t0 = time.perf_counter()
-        m.passo(tok, alvo, k_lr=c["k_lr"])
-        dt = time.perf_counter() - t0
-    finally:
-        ops.BLK = antes
-    # per-layer work dominates; embedding/logits (1 of ~13 layer-equivalents) are counted with the layers
-    escala = (c["L"] / L_am)
-    tps = Bt_am * c["T"] / (dt * escala)
-    return tps, dt, torch.get_num_threads(), (f"{L_am} of {c['L']} layers, {Bt_am} of {c['Bt']} sequences of T={c['T']}, int64 torch restatement "
-                                              f"of the spec, {dt:.1f} s; tokens/s scaled by the layer count")
-
-
-def braco_referencia_passo(args):
-    rank, _, _ = dist_info()
-    if rank != 0:
-        return
-    vals = []
-    for i in range(min(args.warmup, 1) + min(args.steps, 3)):
-        tps, dt, th, txt = cpu_passo_amostra()
-        if i >= min(args.warmup, 1):
-            vals.append((tps, dt))
-    tps = sum(v for v, _ in vals) / len(vals)
-    c = PASSO
-    print(json.dumps({
-        "impl": "reference", "metric": "train_tokens_per_s", "value": tps, "unit": "tokens/s", "n_gpus": args.gpus, "steps": len(vals),
-        "warmup": min(args.warmup, 1), "ms_per_step": 1e3 * sum(d for _, d in vals) / len(vals), "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "int8+int32", "data": "synthetic",
-        "config": {"workload": f"passo_{c['L']}L_D{c['D']}_H{c['H']}_T{c['T']}_Bt{c['Bt']}_b{BLK}", "sample": txt},
-        "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": th, "kind": "port", "sample": txt},
-        "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}))
-
-
-def resumo_perfil(reg, pk):
-    """Per-operation GPU time of one eager step (CUDA events around every launch) and the roofline of the GEMMs."""
-    tempos, ops_gemm, ms_gemm = {}, 0.0, 0.0
+def resumo_perfil(reg):
+    """Per-operation GPU time of one eager step (CUDA events around every launch), operation count and algorithmic bytes of its GEMMs."""
+    tempos, ops_gemm, ms_gemm, alg = {}, 0.0, 0.0, 0.0
+    from jatai_b200 import ops
     for (op, ini, fim), lanc in zip(reg.eventos, reg.lancamentos):
         ms = ini.elapsed_time(fim)
         tempos[op] = tempos.get(op, 0.0) + ms
         if op.startswith("gemm"):
             a, b = lanc["entradas"]["A"], lanc["entradas"]["B"]
             ops_gemm += 2.0 * a.shape[0] * a.shape[1] * b.shape[0]
+            alg += bytes_gemm(a.shape[0], a.shape[1], b.shape[0], ops.BLK, op == "gemm_cru")
             ms_gemm += ms
-    total = sum(tempos.values())
     ordem = sorted(tempos.items(), key=lambda kv: -kv[1])
-    return {"ms_per_op": {k: round(v, 4) for k, v in ordem}, "ms_total": total, "gemm_ops": ops_gemm, "gemm_ms": ms_gemm}
+    return {"ms_per_op": {k: round(v, 4) for k, v in ordem}, "ms_total": sum(tempos.values()), "gemm_ops": ops_gemm, "gemm_ms": ms_gemm, "gemm_bytes": alg}
 
 
 def tempo_gemms(oc, reg):
@@ -392,7 +517,7 @@ def tempo_gemms(oc, reg):
     roda()
     torch.cuda.synchronize()
     st, gr = torch.cuda.Stream(), torch.cuda.CUDAGraph()
-    ini, fim = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ini, fim = ev(), ev()
     with torch.cuda.stream(st):
         try:
             with torch.cuda.graph(gr, stream=st):
@@ -410,115 +535,178 @@ def tempo_gemms(oc, reg):
     return ini.elapsed_time(fim) / reps, len(chamadas)
 
 
-def braco_passo(args):
-    rank, local, mundo = dist_info()
-    if mundo > 1:
-        torch.cuda.set_device(local)
-        torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", local))
-    dev = torch.device("cuda", local if mundo > 1 else 0)
-    torch.cuda.set_device(dev)
-    from jatai_b200 import modelo, ops, paralelo, registro
-    ops.define_blk(BLK)
-    c = PASSO
-    reg = registro.Registro(tempfile.mkdtemp(), f"passo{rank}", eco=False, salvar=False)
-    oc = ops.OpsCuda(reg)
-    if args.via is not None:
-        assert oc.lib.jt_gemm_via(args.via) == 0
+def digest_estado(m):
+    """SHA-256 over weights, momentum and residual (mantissas and exponents, in name order)."""
+    h = hashlib.sha256()
+    for n in sorted(m.p):
+        for par in (m.p[n], m.mom[n], m.res[n]):
+            for t in par:
+                h.update(t.detach().cpu().numpy().tobytes())
+    return h.digest()
+
+
+def mede_passo(c, rank, mundo, dev, steps, warmup, via=None, eager=False, biblioteca=None, perfil=True, e2e=True, gemms=False):
+    """One configuration of the training step: eager steps (workspace sizing, per-op profile), graph capture, timed replays
+    with device-resident tokens, then the same through host buffers.  Returns a dict of measurements."""
+    from jatai_b200 import modelo, paralelo
+    ops, oc, reg = lanca_ops(c["blk"], f"passo{rank}", biblioteca)
+    if via is not None:
+        assert oc.lib.jt_gemm_via(via) == 0
     red = paralelo.Redutor() if mundo > 1 else None
     m = modelo.Modelo(c["V"], c["D"], c["H"], c["FF"], c["L"], 0, dev, oc, reg, redutor=red)
     Bt, T = c["Bt"], c["T"]
     lotes = [tuple(t.to(dev) for t in lote_tokens(100 * rank + i, Bt, T, c["V"])) for i in range(8)]
-    # one eager step with per-launch events: sizes the attention workspace, gives the per-op breakdown
+    r = {}
     reg.novo_passo(0)
     m.passo(*lotes[0], k_lr=c["k_lr"])                # first step pays the one-time costs (workspace, kernel attributes)
     reg.fim_passo()
-    reg.perfil = True
+    reg.perfil = perfil
     reg.novo_passo(1)
     m.passo(*lotes[1], k_lr=c["k_lr"])
     reg.fim_passo()
-    perfil = resumo_perfil(reg, picos())
-    lancamentos = len(reg.lancamentos)
+    r["lancamentos"] = len(reg.lancamentos)
+    if perfil:
+        r["perfil"] = resumo_perfil(reg)
     reg.perfil = False
     reg.tempos = {}
-    gemm_ms, n_gemms = tempo_gemms(oc, reg)
-    passo_fn = None
-    modo = "eager"
-    if not args.eager:
+    if gemms:
+        r["gemm_ms"], r["n_gemms"] = tempo_gemms(oc, reg)
+    passo_fn, modo = None, "eager"
+    if not eager:
         try:
-            gravado = modelo.PassoGravado(m, Bt, T, c["k_lr"])
-            passo_fn, modo = gravado, "cuda_graph"
-        except Exception as e:          # capture refused (e.g. a collective that can not be captured): run eagerly, say so
-            modo = f"eager (graph capture failed: {type(e).__name__})"
+            passo_fn, modo = modelo.PassoGravado(m, Bt, T, c["k_lr"]), "cuda_graph"
+        except Exception as e:          # capture refused: run eagerly, say so
+            modo = f"eager (graph capture failed: {type(e).__name__}: {e})"
     if passo_fn is None:
         def passo_fn(tok, alvo):
             reg.lancamentos = []
             return m.passo(tok, alvo, k_lr=c["k_lr"])
-    ev = lambda: torch.cuda.Event(enable_timing=True)
-    W = max(args.warmup, 3)
-    for i in range(W):
+    r["modo"] = modo
+    for i in range(warmup):
         passo_fn(*lotes[i % 8])
     barreira(mundo)
     rel = Relogios(dev.index or 0)
     ini, fim = ev(), ev()
     ini.record()
-    for i in range(args.steps):
+    for i in range(steps):
         perda = passo_fn(*lotes[i % 8])
     fim.record()
     barreira(mundo)
-    ms = max_ranks(ini.elapsed_time(fim), mundo, dev) / args.steps
-    clocks = rel.fim()
-    n_err = reg.lib.jt_erro_le((ctypes.c_longlong * 6)())
-    assert n_err == 0, f"device error record has {n_err} events"
-    tps = mundo * Bt * T / (ms * 1e-3)
-    # end to end: tokens come from pinned host memory every step and the loss is read back every step
-    hospedeiro = [tuple(t.pin_memory() for t in lote_tokens(100 * rank + i, Bt, T, c["V"])) for i in range(8)]
-    perdas = []
+    r["ms"] = max_ranks(ini.elapsed_time(fim), mundo, dev) / steps
+    r["clocks"] = rel.fim()
+    sem_erros(reg, nome_passo(c))
+    r["tps"] = mundo * Bt * T / (r["ms"] * 1e-3)
+    r["perda"] = float(perda)
+    if e2e:
+        # end to end: tokens come from pinned host memory every step and the loss is read back every step
+        hospedeiro = [tuple(t.pin_memory() for t in lote_tokens(100 * rank + i, Bt, T, c["V"])) for i in range(8)]
 
-    def passo_e2e(i):
-        tok, alvo = hospedeiro[i % 8]
-        p = passo_fn(tok.to(dev, non_blocking=True), alvo.to(dev, non_blocking=True))
-        perdas.append(float(p))                      # device -> host read of the step's result (synchronises)
+        def passo_e2e(i):
+            tok, alvo = hospedeiro[i % 8]
+            return float(passo_fn(tok.to(dev, non_blocking=True), alvo.to(dev, non_blocking=True)))      # device -> host read (synchronises)
 
-    for i in range(2):
-        passo_e2e(i)
-    barreira(mundo)
-    ini.record()
-    for i in range(args.steps):
-        passo_e2e(i)
-    fim.record()
-    barreira(mundo)
-    ms_e2e = max_ranks(ini.elapsed_time(fim), mundo, dev) / args.steps
-    perda_f = float(perda)
+        for i in range(2):
+            passo_e2e(i)
+        barreira(mundo)
+        ini.record()
+        for i in range(steps):
+            passo_e2e(i)
+        fim.record()
+        barreira(mundo)
+        r["ms_e2e"] = max_ranks(ini.elapsed_time(fim), mundo, dev) / steps
+        r["tps_e2e"] = mundo * Bt * T / (r["ms_e2e"] * 1e-3)
+        r["h2d"], r["d2h"] = 2 * Bt * T * 8, 8
+    if red is not None:
+        # every rank applied the same update to the same sums: the training state must be identical everywhere
+        meu = torch.tensor(list(digest_estado(m)), dtype=torch.uint8, device=dev)
+        todos = [torch.empty_like(meu) for _ in range(mundo)]
+        torch.distributed.all_gather(todos, meu)
+        r["estado_igual"] = all(torch.equal(t, todos[0]) for t in todos)
+        r["fio"] = {"collectives_per_step": getattr(passo_fn, "coletivos_por_passo", None), "max_bytes_per_step": int(red._max.numel()),
+                    "sum_bytes_per_step": int(getattr(red, "bytes_soma_passo", 0) or red._plano.numel() * 4)}
+    del passo_fn, m, lotes
+    torch.cuda.synchronize()
+    torch.cuda.empty_cache()
+    return r
+
+
+def braco_passo(args):
+    rank, mundo, dev = inicia_gpu()
+    c = CONFIGS[args.config]
+    pk = picos()
+    W = max(args.warmup, 3)
+    r = mede_passo(c, rank, mundo, dev, args.steps, W, via=args.via, eager=args.eager, gemms=True)
+    Bt, T = c["Bt"], c["T"]
+    pf = r["perfil"]
+    ach = pf["gemm_ops"] / (r["gemm_ms"] * 1e-3) / 1e12 if r.get("gemm_ms") else None
+    pico_b, pico_s = 2.0 * pk["bf16"], 2.0 * pk["bf16_sust"]
+    saida = {
+        "metric": "train_tokens_per_s", "value": r["tps"], "unit": "tokens/s", "n_gpus": mundo, "steps": args.steps, "warmup": W,
+        "ms_per_step": r["ms"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8+int32", "data": "synthetic",
+        "config": {"workload": nome_passo(c), "tokens_per_gpu_step": Bt * T, "global_tokens_per_step": mundo * Bt * T, "block": c["blk"],
+                   "mode": r["modo"], "parallelism": f"dp{mundo}",
+                   "l2": "weights + momentum + residual + activations of a step exceed L2 (about 0.6 GB touched per step at the smallest configuration)",
+                   "init": "seeded random weights (reference recipe), uniform random byte tokens"},
+        "roofline": {"bound": "tensor", "achieved": ach, "peak": pico_s, "unit": "TOPS", "frac": (ach / pico_s) if ach else None,
+                     "frac_of_2x_bf16_burst": (ach / pico_b) if ach else None,
+                     "traffic": TRAFEGO_NCU["bytes"] * pf["gemm_bytes"] / bytes_gemm(*TRAFEGO_NCU["forma"], BLK, False) if mundo == 1 else None,
+                     "traffic_source": TRAFEGO_NCU["fonte"] + "; scaled to the step's GEMM launches by their algorithmic bytes (cold-L2 figure: inside the step most operands are still in L2)",
+                     "algorithmic_bytes": pf["gemm_bytes"],
+                     "kernel": f"all {r.get('n_gemms')} block GEMMs of one step (k_gemm_tc), issued back to back from one CUDA graph with the step's own operands",
+                     "peak_source": f"2 x cuBLAS bf16 sustained ({pk['origem']}); frac_of_2x_bf16_burst uses the burst figure", "gemm_ms_per_step": r.get("gemm_ms")},
+        "clocks": r["clocks"],
+        "e2e": {"value": r["tps_e2e"], "unit": "tokens/s", "h2d_bytes_per_step": r["h2d"], "d2h_bytes_per_step": r["d2h"],
+                "ms_per_step": r["ms_e2e"], "includes": "tokens and targets from pinned host memory, the step, loss read back to the host every step"},
+        "gpu_launches": r["lancamentos"] * args.steps,
+        "extra": {"launches_per_step": r["lancamentos"], "loss_last": r["perda"], "ms_per_op_eager": pf["ms_per_op"]},
+    }
+    if mundo > 1:
+        saida["extra"]["dp_state_identical"] = r["estado_igual"]
+        saida["extra"]["wire"] = r["fio"]
+    ex = saida["extra"]
+    if not args.sem_extras:
+        def tenta(nome, f):
+            t0 = time.perf_counter()
+            try:
+                ex[nome] = f()
+            except Exception as e:            # an extra leg never takes the headline down with it
+                ex[nome] = {"failed": f"{type(e).__name__}: {e}"}
+            if isinstance(ex[nome], dict):
+                ex[nome]["leg_seconds"] = round(time.perf_counter() - t0, 1)
+            torch.cuda.empty_cache()
+
+        if args.config != "c5":
+            def perna5():
+                c5 = CONFIGS["c5"]
+                r5 = mede_passo(c5, rank, mundo, dev, steps=3, warmup=1, via=args.via)
+                d = {"workload": nome_passo(c5), "tokens_per_s": r5["tps"], "ms_per_step": r5["ms"], "e2e_tokens_per_s": r5["tps_e2e"], "steps": 3, "warmup": 1,
+                     "mode": r5["modo"], "parallelism": f"dp{mundo}", "tokens_per_gpu_step": c5["Bt"] * c5["T"], "launches_per_step": r5["lancamentos"],
+                     "loss_last": r5["perda"], "ms_per_op_eager": r5["perfil"]["ms_per_op"], "clocks": r5["clocks"]}
+                if mundo > 1:
+                    d["dp_state_identical"], d["wire"] = r5["estado_igual"], r5["fio"]
+                return d
+            tenta("config5", perna5)
+        if mundo == 1:
+            def perna2():
+                _, oc, reg = lanca_ops(BLK, "sweep")
+                return mede_sweep(oc, reg, dev)
+            tenta("config2", perna2)
+            tenta("config3", lambda: mede_ops(dev, reps=8, warmup=3))
+            if args.config != "compat":
+                def perna_c():
+                    cc = CONFIGS["compat"]
+                    rc = mede_passo(cc, 0, 1, dev, steps=10, warmup=3, perfil=False, e2e=False)
+                    return {"workload": nome_passo(cc), "tokens_per_s": rc["tps"], "ms_per_step": rc["ms"], "launches_per_step": rc["lancamentos"], "mode": rc["modo"],
+                            "note": "the reference library's own model size and tensor format (block 128, head dimension 4, T=128), on this library; "
+                                    "`--impl reference` reports the reference's dp4a kernels on the same configuration"}
+                tenta("compat", perna_c)
     if mundo > 1:
         torch.distributed.destroy_process_group()
     if rank != 0:
         return
-    pk = picos()
-    pico_i8 = 2.0 * pk["bf16_sust"] if pk.get("bf16_sust") else 2.0 * pk["bf16"]
-    ach = perfil["gemm_ops"] / (gemm_ms * 1e-3) / 1e12 if gemm_ms else None
-    saida = {
-        "metric": "train_tokens_per_s", "value": tps, "unit": "tokens/s", "n_gpus": mundo, "steps": args.steps, "warmup": W,
-        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8+int32", "data": "synthetic",
-        "config": {"workload": f"passo_{c['L']}L_D{c['D']}_H{c['H']}_T{c['T']}_Bt{c['Bt']}_b{BLK}", "tokens_per_gpu_step": Bt * T,
-                   "global_tokens_per_step": mundo * Bt * T, "block": BLK, "mode": modo, "parallelism": f"dp{mundo}",
-                   "l2": "weights + momentum + residual + activations of a step exceed L2 (about 0.6 GB touched per step)",
-                   "init": "seeded random weights (reference recipe), uniform random byte tokens"},
-        "loss_last": perda_f, "launches_per_step": lancamentos,
-        "roofline": {"bound": "tensor", "achieved": ach, "peak": pico_i8, "unit": "TOPS", "frac": (ach / pico_i8) if ach else None,
-                     "traffic": TRAFEGO_GEMMS_PASSO if (mundo == 1 and args.via is None and BLK == 32) else None,
-                     "traffic_note": "DRAM bytes read + written by the step's 148 GEMM launches, one ncu pass (cold L2 per launch; the outputs stay in L2): profiles/k_gemm_tc_b32.md",
-                     "kernel": f"all {n_gemms} block GEMMs of one step (k_gemm_tc), issued back to back from one CUDA graph with the step's own operands",
-                     "peak_source": f"2 x cuBLAS bf16 sustained ({pk['origem']})", "gemm_ms_per_step": gemm_ms},
-        "ms_per_op_eager": perfil["ms_per_op"], "clocks": clocks,
-        "e2e": {"value": mundo * Bt * T / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": 2 * Bt * T * 8, "d2h_bytes_per_step": 8,
-                "ms_per_step": ms_e2e, "includes": "tokens and targets from pinned host memory, the step, loss read back to the host every step"},
-        "gpu_launches": lancamentos * args.steps,
-    }
-    if red is not None:
-        saida["wire"] = {"collectives_per_step": 1 + (len(passo_fn._fatias) if modo == "cuda_graph" else 1), "max_bytes_per_step": int(red._max.numel()), "sum_bytes_per_step": int(red._plano.numel()) * 4}
     if mundo == 1 and not args.sem_cpu:
         try:
-            ctps, dt, th, txt = cpu_passo_amostra()
+            ctps, dt, th, txt = cpu_passo_amostra(c)
             saida["cpu_baseline"] = {"value": ctps, "unit": "tokens/s", "cores": th, "kind": "port", "sample": txt}
         except Exception as e:
             saida["cpu_baseline"] = {"value": None, "unit": "tokens/s", "cores": 0, "kind": "port", "sample": f"failed: {e}"}
@@ -526,17 +714,10 @@ def braco_passo(args):
 
 
 # ------------------------------------------------------------------------------------------------ fused op suite
-def braco_ops(args):
+def mede_ops(dev, reps=12, warmup=3):
     """Benchmark configuration 3: the bandwidth-bound ops at 16384 tokens x D=1024 (block 32); achieved HBM GB/s per op from
     the algorithmic bytes (inputs read once + outputs written once).  Inputs rotate over enough copies to exceed L2."""
-    rank, local, mundo = dist_info()
-    dev = torch.device("cuda", local if mundo > 1 else 0)
-    torch.cuda.set_device(dev)
-    from jatai_b200 import ops, registro
-    ops.define_blk(BLK)
-    reg = registro.Registro(tempfile.mkdtemp(), f"ops{rank}", eco=False, salvar=False)
-    oc = ops.OpsCuda(reg)
-    reg.novo_passo(0)
+    ops, oc, reg = lanca_ops(BLK, "ops")
     M, D, FF, V, NW = 16384, 1024, 4096, 256, 12 * 1024 * 1024
     g = torch.Generator().manual_seed(7)
 
@@ -578,17 +759,21 @@ def braco_ops(args):
     res = copias(lambda: bloco(3072, 4096, e0=-20), 3)
     casos_.append(("momento", NW * (6 + 2 * b1), [lambda a=a, b=b: oc.momento(a, b) for a, b in zip(gw, mom)]))
     casos_.append(("peso", NW * 5 * b1, [lambda a=a, b=b, r=r: oc.peso(a, b, r, 4, True) for a, b, r in zip(w, mom, res)]))
+    casos_.append(("momento_peso (one launch)", NW * (6 + 7 * b1), [lambda a=a, b=b, ww=ww, r=r: oc.momento_peso(a, b, ww, r, 4, True) for a, b, ww, r in zip(gw, mom, w, res)]))
     Bt, T, H = 16, 1024, 16
     qkv = copias(lambda: bloco(M, 3 * D, esp=3), 2)
-    casos_.append(("atencao (16 seq x 16 heads x T=1024, hd 64)", M * 3 * D * b1 + M * D * 6 + Bt * H * T * T,
-                   [lambda t=t: oc.atencao(t, Bt, T, H) for t in qkv]))
+    b_at = M * 3 * D * b1 + M * D * 6 + Bt * H * T * T
+    casos_.append(("atencao (16 seq x 16 heads x T=1024, hd 64)", b_at, [lambda t=t: oc.atencao(t, Bt, T, H) for t in qkv]))
+    saidas_at = [oc.atencao(t, Bt, T, H) for t in qkv]
+    go = copias(lambda: bloco(M, D, e0=-20), 2)
+    casos_.append(("atencao_back (same shape)", M * 3 * D * b1 + M * D * b1 + Bt * H * T * T + M * 3 * D * 6,
+                   [lambda t=t, gg=gg, s=s: oc.atencao_back(gg, t, s[1], Bt, T, H) for t, gg, s in zip(qkv, go, saidas_at)]))
     pk = picos()
-    ev = lambda: torch.cuda.Event(enable_timing=True)
     tabela, tot_b, tot_ms = {}, 0.0, 0.0
-    reps = max(args.steps, 5)
     corrente = torch.cuda.Stream()
+    n_lanc = 0
     for nome, nbytes, fs in casos_:
-        for i in range(max(args.warmup, 3)):
+        for i in range(warmup):
             reg.lancamentos = []
             fs[i % len(fs)]()
         torch.cuda.synchronize()
@@ -614,22 +799,32 @@ def braco_ops(args):
         ms = a.elapsed_time(b) / reps
         gbs = nbytes / (ms * 1e-3) / 1e9
         tabela[nome] = {"ms": round(ms, 4), "MB": round(nbytes / 1e6, 1), "GB/s": round(gbs, 1), "frac_of_measured_hbm": round(gbs / pk["hbm_gbs"], 3)}
-        tot_b += nbytes
-        tot_ms += ms
-    n = reg.lib.jt_erro_le((ctypes.c_longlong * 6)())
-    assert n == 0, f"device error record has {n} events"
+        n_lanc += reps
+        if not nome.startswith("atencao"):             # the attention kernels are contractions, not bandwidth ops: listed, not aggregated
+            tot_b += nbytes
+            tot_ms += ms
+    sem_erros(reg, "config3")
+    agg = tot_b / (tot_ms * 1e-3) / 1e9
+    return {"per_op": tabela, "aggregate_GBs": agg, "aggregate_frac_of_measured_hbm": agg / pk["hbm_gbs"], "hbm_peak_GBs": pk["hbm_gbs"],
+            "peak_source": f"STREAM-style copy ({pk['origem']})", "reps": reps, "ms_total": tot_ms, "launches": n_lanc,
+            "workload": "ops_16384tok_D1024_b32", "l2": "inputs rotate over copies totalling more than L2 (126 MB)",
+            "timing": "each op recorded `reps` times in a CUDA graph over rotating inputs; the replay is timed with CUDA events",
+            "aggregate_note": "bandwidth ops only; the two attention lines are contractions and are listed for their time"}
+
+
+def braco_ops(args):
+    rank, mundo, dev = inicia_gpu()
+    r = mede_ops(dev, reps=max(args.steps, 5), warmup=max(args.warmup, 3))
     if rank != 0:
         return
-    agg = tot_b / (tot_ms * 1e-3) / 1e9
     print(json.dumps({
-        "metric": "fused_ops_hbm_gbs", "value": agg, "unit": "GB/s", "n_gpus": 1, "steps": reps, "warmup": max(args.warmup, 3), "ms_per_step": tot_ms,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8+int32", "data": "synthetic",
-        "config": {"workload": "ops_16384tok_D1024_b32", "l2": "inputs rotate over copies totalling more than L2 (126 MB)",
-                   "timing": "each op recorded `steps` times in a CUDA graph over rotating inputs; the replay is timed with CUDA events"},
-        "per_op": tabela,
-        "roofline": {"bound": "hbm", "achieved": agg, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": agg / pk["hbm_gbs"], "traffic": None,
-                     "peak_source": f"STREAM-style copy ({pk['origem']})"},
-        "gpu_launches": reps * len(casos_)}))
+        "metric": "fused_ops_hbm_gbs", "value": r["aggregate_GBs"], "unit": "GB/s", "n_gpus": 1, "steps": r["reps"], "warmup": max(args.warmup, 3),
+        "ms_per_step": r["ms_total"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8+int32", "data": "synthetic",
+        "config": {"workload": r["workload"], "l2": r["l2"], "timing": r["timing"]},
+        "per_op": r["per_op"],
+        "roofline": {"bound": "hbm", "achieved": r["aggregate_GBs"], "peak": r["hbm_peak_GBs"], "unit": "GB/s", "frac": r["aggregate_frac_of_measured_hbm"],
+                     "traffic": None, "peak_source": r["peak_source"]},
+        "gpu_launches": r["launches"]}))
 
 
 def main():
@@ -639,15 +834,17 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="passo", choices=["gemm", "passo", "ops"])
+    ap.add_argument("--config", default="c4", choices=sorted(CONFIGS), help="passo: which configuration is the headline")
     ap.add_argument("--via", type=int, default=None, help="force a GEMM path (jt_gemm_via)")
     ap.add_argument("--eager", action="store_true", help="passo: no CUDA graph")
     ap.add_argument("--forma", type=int, nargs=3, default=None, metavar=("M", "K", "N"), help="gemm: another shape (profiling captures)")
     ap.add_argument("--sem-cpu", dest="sem_cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--sem-extras", dest="sem_extras", action="store_true", help="passo: headline only, no extra legs")
     args = ap.parse_args()
     if args.forma:
         FORMA.update(M=args.forma[0], K=args.forma[1], N=args.forma[2])
     if args.impl == "reference":
-        return braco_referencia_passo(args) if args.workload == "passo" else braco_referencia(args)
+        return braco_referencia_passo(args) if args.workload == "passo" else braco_referencia_gemm(args)
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (there is no CPU path)")
     if args.workload == "passo":

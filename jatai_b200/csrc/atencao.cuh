@@ -534,24 +534,37 @@ inline size_t smem_colunas(int HD) { return 4 * ((size_t)TI * (HD + 4) + 2 * TJ 
 
 }  // namespace at
 
-// workspace of the attention backward: statistics + s_lin, grown on demand (never inside a stream capture:
-// run one step eagerly before capturing, as the reference's training loop does)
-static int* g_at_ws = nullptr;
-static size_t g_at_ws_ints = 0;
+// Workspace of the attention backward (statistics, s_lin, the T x T matrices), one per device, grown on demand.
+// A superseded buffer is never freed: a CUDA graph recorded earlier may still hold its address.  Growth needs
+// cudaMalloc, which a stream capture does not allow: a call that would have to grow while its stream is capturing is
+// refused (cudaErrorStreamCaptureUnsupported); run one step eagerly before capturing, as the reference's loop does.
+constexpr int AT_MAX_DEV = 64;
+static int* g_at_ws[AT_MAX_DEV];
+static size_t g_at_ws_ints[AT_MAX_DEV];
+
+static int at_dispositivo(int* dev) {
+    cudaError_t c = cudaGetDevice(dev);
+    if (c != cudaSuccess) return (int)c;
+    return (*dev < 0 || *dev >= AT_MAX_DEV) ? (int)cudaErrorInvalidDevice : 0;
+}
 
 static int at_log2(int x) { int k = 0; while ((1 << k) < x) k++; return (1 << k) == x ? k : -1; }
 
 // raises a kernel's dynamic shared-memory limit; remembered per kernel, so a repeated launch makes no runtime call
 static cudaError_t at_smem_ptr(const void* kern, size_t bytes) {
     static const void* quem[64];
+    static int onde[64];                  // the attribute belongs to (kernel, device)
     static size_t quanto[64];
     static int n = 0;
-    int i = 0;
-    while (i < n && quem[i] != kern) i++;
-    if (i < n && bytes <= quanto[i]) return cudaSuccess;
-    cudaError_t c = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    int dev = 0;
+    cudaError_t c = cudaGetDevice(&dev);
     if (c != cudaSuccess) return c;
-    if (i == n && n < 64) { quem[n] = kern; n++; }
+    int i = 0;
+    while (i < n && !(quem[i] == kern && onde[i] == dev)) i++;
+    if (i < n && bytes <= quanto[i]) return cudaSuccess;
+    c = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (c != cudaSuccess) return c;
+    if (i == n && n < 64) { quem[n] = kern; onde[n] = dev; n++; }
     if (i < 64) quanto[i] = bytes;
     return cudaSuccess;
 }
@@ -620,15 +633,18 @@ static int atencao_tras(int blk, const int8_t* gom, const int8_t* goE, const int
     const size_t base = (size_t)Bt * H * (at::N_EST + T), matriz = (size_t)Bt * H * T * T;
     const bool com_matriz = matriz <= ((size_t)1 << 28);
     const size_t precisa = base + (com_matriz ? matriz : 0);
-    if (precisa > g_at_ws_ints) {
-        if (g_at_ws) cudaFree(g_at_ws);
-        g_at_ws = nullptr;
-        g_at_ws_ints = 0;
-        cudaError_t c = cudaMalloc(&g_at_ws, precisa * sizeof(int));
+    int dev = 0;
+    if (int r = at_dispositivo(&dev)) return r;
+    if (precisa > g_at_ws_ints[dev]) {
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(st, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) return (int)cudaErrorStreamCaptureUnsupported;
+        int* novo = nullptr;
+        cudaError_t c = cudaMalloc(&novo, precisa * sizeof(int));
         if (c != cudaSuccess) return (int)c;
-        g_at_ws_ints = precisa;
+        g_at_ws[dev] = novo;              // the old buffer stays allocated until the process exits
+        g_at_ws_ints[dev] = precisa;
     }
-    return atencao_tras_ws(blk, gom, goE, qm, qE, P, Gacc, Ge, Bt, T, H, D, GA, limite, kid, st, g_at_ws, com_matriz);
+    return atencao_tras_ws(blk, gom, goE, qm, qE, P, Gacc, Ge, Bt, T, H, D, GA, limite, kid, st, g_at_ws[dev], com_matriz);
 }
 
 }  // namespace jt

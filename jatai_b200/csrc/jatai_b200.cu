@@ -64,9 +64,12 @@ static bool faz_mapa(CUtensorMap* m, const void* p, int linhas, int K, int linha
 template <int BLK, int MODO, int VIA, int TNv>
 static int lanca_tc(const CUtensorMap& mA, const CUtensorMap& mB, const int8_t* EA, const int8_t* EB, const int8_t* RA, const int8_t* RB,
                     const SaidaGemm& S, int M, int N, int K, int partes, int kid) {
-    static bool pronto = false;
+    static bool feito[64];                 // kernel attributes are per device
     using C_ = tc::Cfg<TNv>;
     auto k = tc::k_gemm_tc<BLK, MODO, VIA, TNv>;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return (int)cudaErrorInvalidDevice;
+    bool& pronto = feito[dev];
     if (!pronto) {
         cudaError_t c = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C_::SMEM_BYTES);
         if (c != cudaSuccess) return (int)c;
@@ -103,8 +106,9 @@ static int gemm_blk(const int8_t* A, const int8_t* EA, const int8_t* B, const in
     const bool estreito = BLK == 32 && usa_tc && g_tn != 128 && (g_tn == 64 || 2 * tiles128 <= 148 || r64 < r128);
     const int tn = estreito ? 64 : TN;
     CUtensorMap mA, mB;
-    if (usa_tc) usa_tc = faz_mapa(&mA, A, M, K) && faz_mapa(&mB, B, N, K, tn);
-    if (!usa_tc && g_via != 0 && g_via != 2) return (int)cudaErrorInvalidValue;     // a forced tensor-core path never falls back silently
+    // a shape the tensor-core kernel takes never falls back silently: a tensor map that can not be encoded is an error
+    if (usa_tc && !(faz_mapa(&mA, A, M, K) && faz_mapa(&mB, B, N, K, tn))) return (int)cudaErrorInvalidValue;
+    if (!usa_tc && g_via != 0 && g_via != 2) return (int)cudaErrorInvalidValue;     // nor does a forced tensor-core path on a shape it can not take
     // split-K (raw output only): powers of two while the grid stays below the target and the K range divides evenly
     const int unidades = usa_tc ? K / tc::KC : K / BLK;            // indivisible K units of the chosen kernel
     const long long tiles = usa_tc ? (long long)(N / tn) * (M / tc::TM) : (long long)(N / TN) * (M / 64);

@@ -341,6 +341,7 @@ class PassoGravado:
             lib.jt_stream(None)
             modelo.estatisticas, self.reg.vigiar, self.reg.perfil = est, vig, perf
         self.lancamentos = list(self.reg.lancamentos)
+        self.coletivos_por_passo = 0 if red is None else 1 + len(self._fatias)
         self.reg.info(f"step recorded in {len(self.grafos)} CUDA graph(s): {len(self.lancamentos)} launches", lancamentos=len(self.lancamentos))
 
     def __call__(self, tok, alvo):

@@ -95,6 +95,11 @@ class OpsCuda:
                 raise RuntimeError(f"library refused block length {BLK}")
         elif BLK != 128:
             raise RuntimeError("this library has a fixed block length of 128; call ops.define_blk(128) first")
+        # a library with only the reference's entry points: the fused extras read as absent, callers fall back to the separate operations
+        for metodo, fn in (("transpoe2", "jt_transpoe2"), ("momento_peso", "jt_momento_peso"), ("rms_back_soma", "jt_rms_back_soma"),
+                           ("max_linha", "jt_max_linha")):
+            if not hasattr(self.lib, fn):
+                setattr(self, metodo, None)
 
     # ------------------------------------------------------------------ plumbing
     def _lanca(self, op, fn, ponteiros, inteiros, entradas, forma, longos=()):

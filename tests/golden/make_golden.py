@@ -55,7 +55,9 @@ def define_blk(O, blk):
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py <reference checkout>")
+    ref = sys.argv[1]
     sys.path.insert(0, os.path.join(ref, "jatai_cuda"))
     import ops as O
     ops = Adaptador(O)
