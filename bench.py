@@ -635,7 +635,7 @@ def braco_passo(args):
     c = CONFIGS[args.config]
     pk = picos()
     W = max(args.warmup, 3)
-    r = mede_passo(c, rank, mundo, dev, args.steps, W, via=args.via, eager=args.eager, gemms=True)
+    r = mede_passo(c, rank, mundo, dev, args.steps, W, via=args.via, eager=args.eager, gemms=True, biblioteca=args.biblioteca)
     Bt, T = c["Bt"], c["T"]
     pf = r["perfil"]
     ach = pf["gemm_ops"] / (r["gemm_ms"] * 1e-3) / 1e12 if r.get("gemm_ms") else None
@@ -840,6 +840,7 @@ def main():
     ap.add_argument("--forma", type=int, nargs=3, default=None, metavar=("M", "K", "N"), help="gemm: another shape (profiling captures)")
     ap.add_argument("--sem-cpu", dest="sem_cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--sem-extras", dest="sem_extras", action="store_true", help="passo: headline only, no extra legs")
+    ap.add_argument("--biblioteca", default=None, help="passo: another library with the same C ABI (diagnostics; block length of --config must suit it)")
     args = ap.parse_args()
     if args.forma:
         FORMA.update(M=args.forma[0], K=args.forma[1], N=args.forma[2])

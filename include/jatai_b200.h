@@ -12,9 +12,13 @@
  *     cudaErrorInvalidValue (1) and launch nothing;
  *   - all launches go to the stream given to jt_stream (NULL = legacy default stream); nothing synchronises
  *     except jt_erro_le and jt_sincroniza, so a whole step can be captured in a CUDA graph;
- *   - every input and output is owned by the caller; the only device memory the library allocates is the
- *     workspace of jt_atencao_back (Bt*H*(8+T+T*T) ints - the T*T part, which carries intermediate matrices between
- *     its kernels, only while it stays below 1 GiB - cudaMalloc on first use, reused and grown afterwards);
+ *   - every input and output is owned by the caller; the only device memory the library allocates is the attention
+ *     workspace, one per device: cudaMalloc the first time a size is seen, reused afterwards, replaced by a larger one when
+ *     needed (never freed: a recorded CUDA graph may hold the old address; growth inside a stream capture is refused with
+ *     cudaErrorStreamCaptureUnsupported, so run one step eagerly before capturing).  Head dimension 64: the split operands
+ *     (384 bytes per token and head in the forward, 640 in the backward) and, in the backward, 2*Bt*H*T*T bytes of dS' digits;
+ *     other head dimensions: Bt*H*(8+T+T*T) ints (the T*T part only below 1 GiB).  Calls that overlap on the GPU share it;
+ *   - host state (stream, block length, paths) is per process; the workspace and kernel attributes are kept per device;
  *   - kernels never trap: a broken invariant is recorded in the device error record and the kernel goes on.
  *
  * Tensor formats (jatai_cuda.cu:3-9):
@@ -89,9 +93,12 @@ int jt_soma16(const void* xm, const void* xE, const void* ym, const void* yE, vo
  * jatai_cuda.cu:16).  Host state, like jt_stream. */
 int jt_blk(int blk);
 int jt_blk_atual(void);
-/* GEMM path: 0 automatic | 1 tensor cores with FFMA rounding (block 32; exact while every K-block product stays
- * below 2^18) | 2 CUDA cores (dp4a) | 3 tensor cores with cvt rounding (what 0 selects when the shape allows). */
+/* GEMM path: 0 automatic | 1 tensor cores, refused (cudaErrorInvalidValue) on a shape they do not take | 2 CUDA cores (dp4a) |
+ * 3 tensor cores with every K-block rounded by a float-to-int conversion (block 32's default rounds with an FMA against
+ * 1.5*2^23 after a range check, and converts only the columns that fail it; both are exact for every input). */
 int jt_gemm_via(int via);
+/* Attention path: 0 automatic (tensor cores when the head dimension is 64) | 1 CUDA-core kernels.  Same bits either way. */
+int jt_atencao_via(int via);
 /* Tile width of the tensor-core GEMM: 0 automatic (64 columns when 128-column tiles would leave most SMs idle, block
  * 32 only) | 64 | 128. */
 int jt_gemm_tn(int tn);

@@ -539,13 +539,26 @@ inline size_t smem_colunas(int HD) { return 4 * ((size_t)TI * (HD + 4) + 2 * TJ 
 // cudaMalloc, which a stream capture does not allow: a call that would have to grow while its stream is capturing is
 // refused (cudaErrorStreamCaptureUnsupported); run one step eagerly before capturing, as the reference's loop does.
 constexpr int AT_MAX_DEV = 64;
-static int* g_at_ws[AT_MAX_DEV];
-static size_t g_at_ws_ints[AT_MAX_DEV];
+static void* g_at_ws[AT_MAX_DEV];
+static size_t g_at_ws_bytes[AT_MAX_DEV];
 
-static int at_dispositivo(int* dev) {
-    cudaError_t c = cudaGetDevice(dev);
+// the current device's workspace, at least `bytes` long (0 = ok, else a cudaError_t)
+static int at_ws(size_t bytes, cudaStream_t st, void** p) {
+    int dev = 0;
+    cudaError_t c = cudaGetDevice(&dev);
     if (c != cudaSuccess) return (int)c;
-    return (*dev < 0 || *dev >= AT_MAX_DEV) ? (int)cudaErrorInvalidDevice : 0;
+    if (dev < 0 || dev >= AT_MAX_DEV) return (int)cudaErrorInvalidDevice;
+    if (bytes > g_at_ws_bytes[dev]) {
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(st, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) return (int)cudaErrorStreamCaptureUnsupported;
+        void* novo = nullptr;
+        c = cudaMalloc(&novo, bytes);
+        if (c != cudaSuccess) return (int)c;
+        g_at_ws[dev] = novo;              // the old buffer stays allocated until the process exits
+        g_at_ws_bytes[dev] = bytes;
+    }
+    *p = g_at_ws[dev];
+    return 0;
 }
 
 static int at_log2(int x) { int k = 0; while ((1 << k) < x) k++; return (1 << k) == x ? k : -1; }
@@ -633,18 +646,9 @@ static int atencao_tras(int blk, const int8_t* gom, const int8_t* goE, const int
     const size_t base = (size_t)Bt * H * (at::N_EST + T), matriz = (size_t)Bt * H * T * T;
     const bool com_matriz = matriz <= ((size_t)1 << 28);
     const size_t precisa = base + (com_matriz ? matriz : 0);
-    int dev = 0;
-    if (int r = at_dispositivo(&dev)) return r;
-    if (precisa > g_at_ws_ints[dev]) {
-        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
-        if (cudaStreamIsCapturing(st, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) return (int)cudaErrorStreamCaptureUnsupported;
-        int* novo = nullptr;
-        cudaError_t c = cudaMalloc(&novo, precisa * sizeof(int));
-        if (c != cudaSuccess) return (int)c;
-        g_at_ws[dev] = novo;              // the old buffer stays allocated until the process exits
-        g_at_ws_ints[dev] = precisa;
-    }
-    return atencao_tras_ws(blk, gom, goE, qm, qE, P, Gacc, Ge, Bt, T, H, D, GA, limite, kid, st, g_at_ws[dev], com_matriz);
+    int* ws = nullptr;
+    if (int r = at_ws(precisa * sizeof(int), st, reinterpret_cast<void**>(&ws))) return r;
+    return atencao_tras_ws(blk, gom, goE, qm, qE, P, Gacc, Ge, Bt, T, H, D, GA, limite, kid, st, ws, com_matriz);
 }
 
 }  // namespace jt

@@ -123,10 +123,41 @@ __device__ __forceinline__ void tmem_le32(uint32_t taddr, uint32_t (&d)[32]) {
         : "memory");
 }
 
+// 16 consecutive columns of this thread's lane from each of two tensor-memory addresses (two K slices); one wait for both
+__device__ __forceinline__ void tmem_le16x2(uint32_t ta, uint32_t tb, uint32_t (&a)[16], uint32_t (&b)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%32];\n"
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%33];\n"
+        "tcgen05.wait::ld.sync.aligned;\n"
+        : JT_O16(a, 0), JT_O16(b, 0)
+        : "r"(ta), "r"(tb)
+        : "memory");
+}
+// two fp32 lanes per instruction (fma.rn.f32x2): the align/round loop is bound by instruction issue, not by the FMA pipe
+__device__ __forceinline__ uint64_t par(uint32_t lo, uint32_t hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+    return r;
+}
+__device__ __forceinline__ uint64_t par_f(float lo, float hi) { return par(__float_as_uint(lo), __float_as_uint(hi)); }
+__device__ __forceinline__ void separa(uint64_t v, uint32_t& lo, uint32_t& hi) { asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(v)); }
+__device__ __forceinline__ uint64_t ffma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+
 __device__ __forceinline__ float pot2(int e) { return __int_as_float((127 + e) << 23); }      // 2^e, -126 <= e <= 127
 
-// VIA 0: round with one FFMA against 1.5*2^23 and add the bit pattern (valid while |p * 2^(4-s)| < 2^22);
-// VIA 1: exact float product, cvt.rni to int (valid for every input).
+// How a K-block's partial product p (exact int32 from tensor memory, |p| <= 32 * 127^2 < 2^19) becomes rnd(p << 4, sa + sb):
+// VIA 1 (block 32): p is biased into a float by an integer add of the pattern of 1.5*2^23 + 2^18, one FMA removes the bias and
+//        scales by 2^(4-sa) (exact), a second FMA against 1.5*2^23 scales by 2^-sb and rounds half to even in its single
+//        rounding; the result's bit pattern is added to the accumulator (the pattern of the constant times the slice count comes
+//        off at the end).  Two slices are drained together so that one three-input add serves both, and the FMAs are the packed
+//        two-lane form.  The rounding is exact while |p * 2^(4-s)| < 2^22, i.e. always except s = 0 with |p| >= 2^18; that case is
+//        found by OR-ing the biased patterns (bits 19.. differ from the constant's exactly when |p| >= 2^18; this is what the extra
+//        2^18 in the bias is for) and the 16 columns at hand are then rounded by VIA 2's conversion, for the whole warp.
+// VIA 2: exact float product, cvt.rni to int (valid for every input; block 128, where four MMAs accumulate before a drain).
 template <int BLK, int MODO, int VIA, int TNv>
 __global__ void __launch_bounds__(Cfg<TNv>::N_THR, Cfg<TNv>::CTAS_SM) k_gemm_tc(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                                                       const int8_t* __restrict__ EA, const int8_t* __restrict__ EB,
@@ -311,6 +342,80 @@ __global__ void __launch_bounds__(Cfg<TNv>::N_THR, Cfg<TNv>::CTAS_SM) k_gemm_tc(
         for (int j = 0; j < 32; j++) acc[j] = 0;
         int f = 0;
         bool ok = true;
+        constexpr bool PARES = BLK == 32 && VIA == 1;
+        if constexpr (PARES) {
+            static_assert(NQ == NTM, "one tensor-memory stage per K-block of a chunk");
+            constexpr uint32_t VIES = MAGIA + (1u << 18);                 // pattern of 1.5*2^23 + 2^18
+            constexpr float VIES_F = MAGIA_F + 262144.0f;
+            const uint64_t magia2 = par_f(MAGIA_F, MAGIA_F);
+            for (int c = 0; c < pedacos_por_parte && ok; c++) {
+                const int sl = c % NTB;
+                if (c + 1 < pedacos_por_parte) eaw_prox = le_exp(c + 1);
+                ok = __all_sync(FULL, espera(bar_bfull + 8 * sl, (c / NTB) & 1, aborta, kid, 6));
+                if (!ok) break;
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    const int t0 = 2 * h, t1 = 2 * h + 1;
+                    ok = __all_sync(FULL, espera(bar_tfull + 8 * t0, c & 1, aborta, kid, 4) && espera(bar_tfull + 8 * t1, c & 1, aborta, kid, 4));
+                    if (!ok) break;
+                    tc_fence_depois();
+                    const int sa0 = min(RA - (int)(int8_t)(eaw >> (16 * h)), 40), sa1 = min(RA - (int)(int8_t)(eaw >> (16 * h + 8)), 40);
+                    const float fa0 = pot2(GG - sa0), fa1 = pot2(GG - sa1);
+                    const uint64_t fa0p = par_f(fa0, fa0), fa1p = par_f(fa1, fa1);
+                    const uint64_t cn0p = par_f(-VIES_F * fa0, -VIES_F * fa0), cn1p = par_f(-VIES_F * fa1, -VIES_F * fa1);
+#pragma unroll
+                    for (int hf = 0; hf < 2; hf++) {
+                        uint32_t d0[16], d1[16];
+                        const uint32_t base = tmem + ((uint32_t)(quarto * 32) << 16) + cg * 32 + hf * 16;
+                        tmem_le16x2(base + t0 * TNv, base + t1 * TNv, d0, d1);
+                        if (hf == 1) {
+                            tc_fence_antes();
+                            __syncwarp();
+                            if (lane == 0) { mbar_arrive(bar_tempty + 8 * t0); mbar_arrive(bar_tempty + 8 * t1); }
+                        }
+                        uint32_t o0 = 0, o1 = 0;
+#pragma unroll
+                        for (int k = 0; k < 16; k += 2) {
+                            d0[k] += VIES; d0[k + 1] += VIES; d1[k] += VIES; d1[k + 1] += VIES;
+                            o0 |= d0[k] | d0[k + 1];
+                            o1 |= d1[k] | d1[k + 1];
+                        }
+                        const bool largo = (sa0 == 0 && (o0 & 0xFFF80000u) != MAGIA) || (sa1 == 0 && (o1 & 0xFFF80000u) != MAGIA);
+                        const float* tb0 = tabB + (sl * 4 + t0) * TNv + cg * 32 + hf * 16;
+                        const float* tb1 = tb0 + TNv;
+                        if (__any_sync(FULL, largo)) {
+                            // some |p| >= 2^18 in a slice this row takes unshifted: the conversion rounds every magnitude
+#pragma unroll
+                            for (int k = 0; k < 16; k++) {
+                                const float g0 = fmaf(__uint_as_float(d0[k]), fa0, -VIES_F * fa0), g1 = fmaf(__uint_as_float(d1[k]), fa1, -VIES_F * fa1);
+                                acc[hf * 16 + k] += __float2int_rn(g0 * tb0[k]) + __float2int_rn(g1 * tb1[k]) + (int)(2u * MAGIA);
+                            }
+                        } else {
+#pragma unroll
+                            for (int k4 = 0; k4 < 4; k4++) {
+                                const ulonglong2 b0 = reinterpret_cast<const ulonglong2*>(tb0)[k4], b1 = reinterpret_cast<const ulonglong2*>(tb1)[k4];
+                                const uint64_t fb0[2] = {b0.x, b0.y}, fb1[2] = {b1.x, b1.y};
+#pragma unroll
+                                for (int k2 = 0; k2 < 2; k2++) {
+                                    const int k = 4 * k4 + 2 * k2;
+                                    const uint64_t r0 = ffma2(ffma2(par(d0[k], d0[k + 1]), fa0p, cn0p), fb0[k2], magia2);
+                                    const uint64_t r1 = ffma2(ffma2(par(d1[k], d1[k + 1]), fa1p, cn1p), fb1[k2], magia2);
+                                    uint32_t x0, y0, x1, y1;
+                                    separa(r0, x0, y0);
+                                    separa(r1, x1, y1);
+                                    acc[hf * 16 + k] += (int)(x0 + x1);
+                                    acc[hf * 16 + k + 1] += (int)(y0 + y1);
+                                }
+                            }
+                        }
+                    }
+                }
+                if (!ok) break;
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_bempty + 8 * sl);
+                eaw = eaw_prox;
+            }
+        } else
         for (int c = 0; c < pedacos_por_parte && ok; c++) {
             const int sl = c % NTB;
             if (c + 1 < pedacos_por_parte) eaw_prox = le_exp(c + 1);
@@ -340,8 +445,7 @@ __global__ void __launch_bounds__(Cfg<TNv>::N_THR, Cfg<TNv>::CTAS_SM) k_gemm_tc(
                     for (int k = 0; k < 4; k++) {
                         const int j = j4 * 4 + k;
                         const float g = fmaf(__int_as_float((int)(d[j] + MAGIA)), fa, cneg);      // = p * 2^(4 - sa), exact
-                        if (VIA == 0) acc[j] += __float_as_int(fmaf(g, fbv[k], MAGIA_F));
-                        else acc[j] += __float2int_rn(g * fbv[k]);
+                        acc[j] += __float2int_rn(g * fbv[k]);
                     }
                 }
             }
@@ -350,7 +454,7 @@ __global__ void __launch_bounds__(Cfg<TNv>::N_THR, Cfg<TNv>::CTAS_SM) k_gemm_tc(
             if (lane == 0) mbar_arrive(bar_bempty + 8 * sl);
             eaw = eaw_prox;
         }
-        if (VIA == 0) {
+        if (PARES) {
             const uint32_t vies = (uint32_t)nfatias * MAGIA;
 #pragma unroll
             for (int j = 0; j < 32; j++) acc[j] = (int)((uint32_t)acc[j] - vies);
@@ -371,4 +475,35 @@ __global__ void __launch_bounds__(Cfg<TNv>::N_THR, Cfg<TNv>::CTAS_SM) k_gemm_tc(
 }
 
 }  // namespace tc
+
+// ---------------------------------------------------------------------------------------------- tensor maps (host)
+// cuTensorMapEncodeTiled through the runtime's driver entry point (no link against libcuda)
+typedef CUresult (*PFN_tmap)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                             const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static PFN_tmap g_tmap = nullptr;
+static bool g_tmap_tentou = false;
+
+static PFN_tmap pega_tmap() {
+    if (!g_tmap_tentou) {
+        g_tmap_tentou = true;
+        void* f = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            g_tmap = (PFN_tmap)f;
+    }
+    return g_tmap;
+}
+
+// 2-D map of an int8 matrix [linhas, K] (K contiguous): box = linhas_caixa rows x 128 bytes, 128-byte swizzle
+static bool faz_mapa(CUtensorMap* m, const void* p, int linhas, int K, int linhas_caixa = tc::TM) {
+    PFN_tmap f = pega_tmap();
+    if (!f) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)linhas};
+    cuuint64_t passos[1] = {(cuuint64_t)K};
+    cuuint32_t caixa[2] = {(cuuint32_t)tc::KC, (cuuint32_t)linhas_caixa};
+    cuuint32_t um[2] = {1, 1};
+    return f(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(p), dims, passos, caixa, um, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 }  // namespace jt

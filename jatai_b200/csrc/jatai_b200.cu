@@ -19,47 +19,21 @@
 #include "gemm_simt.cuh"
 #include "gemm_tc.cuh"
 #include "atencao.cuh"
+#include "atencao_tc.cuh"
 
 using namespace jt;
 
 // ---------------------------------------------------------------------------------------------- host state
 static cudaStream_t g_stream = 0;
 static int g_blk = 32;               // exponent block length: 32 (native) or 128 (the reference's format)
-static int g_via = 0;                // GEMM path: 0 automatic | 1 tensor core, FFMA rounding | 2 CUDA cores | 3 tensor core, cvt rounding
+static int g_via = 0;                // GEMM path: 0 automatic | 1 tensor core (forced) | 2 CUDA cores | 3 tensor core, rounding by conversion
 static int g_alvo_ctas = 148;
+static int g_at_via = 0;             // attention path: 0 automatic (tensor cores at head dimension 64) | 1 CUDA cores
 static int g_tn = 0;                 // tile width of the tensor-core GEMM: 0 automatic | 64 | 128        // split-K of raw GEMMs aims at this many CTAs
 
 static int fim() { return (int)cudaGetLastError(); }
 static unsigned nblocos16(long long n16) { return (unsigned)((n16 + 255) / 256); }
 static unsigned nblocos16u(long long n16, int U) { return (unsigned)((n16 + 256LL * U - 1) / (256LL * U)); }      // U chunks per thread
-
-typedef CUresult (*PFN_tmap)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                             const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-static PFN_tmap g_tmap = nullptr;
-static bool g_tmap_tentou = false;
-
-static PFN_tmap pega_tmap() {
-    if (!g_tmap_tentou) {
-        g_tmap_tentou = true;
-        void* f = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
-            g_tmap = (PFN_tmap)f;
-    }
-    return g_tmap;
-}
-
-// 2-D map of an int8 matrix [linhas, K] (K contiguous): box = linhas_caixa rows x 128 bytes, 128-byte swizzle
-static bool faz_mapa(CUtensorMap* m, const void* p, int linhas, int K, int linhas_caixa = tc::TM) {
-    PFN_tmap f = pega_tmap();
-    if (!f) return false;
-    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)linhas};
-    cuuint64_t passos[1] = {(cuuint64_t)K};
-    cuuint32_t caixa[2] = {(cuuint32_t)tc::KC, (cuuint32_t)linhas_caixa};
-    cuuint32_t um[2] = {1, 1};
-    return f(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(p), dims, passos, caixa, um, CU_TENSOR_MAP_INTERLEAVE_NONE,
-             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
 
 template <int BLK, int MODO, int VIA, int TNv>
 static int lanca_tc(const CUtensorMap& mA, const CUtensorMap& mB, const int8_t* EA, const int8_t* EB, const int8_t* RA, const int8_t* RB,
@@ -120,17 +94,18 @@ static int gemm_blk(const int8_t* A, const int8_t* EA, const int8_t* B, const in
         if (c != cudaSuccess) return (int)c;
     }
     if (usa_tc) {
-        // automatic = cvt rounding (exact for every input); the FFMA rounding is chosen explicitly (jt_gemm_via(1))
+        // block 32: FMA rounding with its range check (exact), or the conversion when asked for (jt_gemm_via(3)); block 128: conversion
 #define JT_TC(MD)                                                                                                    \
     case MD:                                                                                                         \
         if constexpr (BLK == 32) {                                                                                   \
             if (estreito) {                                                                                          \
-                if (g_via == 1) return lanca_tc<32, MD, 0, 64>(mA, mB, EA, EB, RA, RB, S, M, N, K, partes, kid);     \
+                if (g_via == 3) return lanca_tc<32, MD, 2, 64>(mA, mB, EA, EB, RA, RB, S, M, N, K, partes, kid);     \
                 return lanca_tc<32, MD, 1, 64>(mA, mB, EA, EB, RA, RB, S, M, N, K, partes, kid);                     \
             }                                                                                                        \
-            if (g_via == 1) return lanca_tc<32, MD, 0, 128>(mA, mB, EA, EB, RA, RB, S, M, N, K, partes, kid);        \
+            if (g_via == 3) return lanca_tc<32, MD, 2, 128>(mA, mB, EA, EB, RA, RB, S, M, N, K, partes, kid);        \
+            return lanca_tc<32, MD, 1, 128>(mA, mB, EA, EB, RA, RB, S, M, N, K, partes, kid);                        \
         }                                                                                                            \
-        return lanca_tc<BLK, MD, 1, 128>(mA, mB, EA, EB, RA, RB, S, M, N, K, partes, kid);
+        return lanca_tc<BLK, MD, 2, 128>(mA, mB, EA, EB, RA, RB, S, M, N, K, partes, kid);
         switch (modo) { JT_TC(0) JT_TC(1) JT_TC(2) JT_TC(3) JT_TC(4) }
 #undef JT_TC
     }
@@ -356,12 +331,22 @@ int jt_softmax_ce(const void* acc, const void* e, const void* alvo, void* gm, vo
 
 // ---------------------------------------------------------------------------------------------- attention
 int jt_atencao(const void* qm, const void* qE, void* Oacc, void* Oe, void* P, int Bt, int T, int H, int D, int GA, int kid) {
+    if (g_at_via == 0 && Bt > 0 && H > 0 && atc_serve(g_blk, T, H, D))
+        return atencao_frente_tc(g_blk, (const int8_t*)qm, (const int8_t*)qE, (int*)Oacc, (int16_t*)Oe, (uint8_t*)P, Bt, T, H, D, GA, kid, g_stream);
     return atencao_frente(g_blk, (const int8_t*)qm, (const int8_t*)qE, (int*)Oacc, (int16_t*)Oe, (uint8_t*)P, Bt, T, H, D, GA, kid, g_stream);
 }
 int jt_atencao_back(const void* gom, const void* goE, const void* qm, const void* qE, const void* P, void* Gacc, void* Ge, int Bt, int T,
                     int H, int D, int GA, int limite, int kid) {
+    if (g_at_via == 0 && Bt > 0 && H > 0 && atc_serve(g_blk, T, H, D))
+        return atencao_tras_tc(g_blk, (const int8_t*)gom, (const int8_t*)goE, (const int8_t*)qm, (const int8_t*)qE, (const uint8_t*)P, (int*)Gacc,
+                               (int16_t*)Ge, Bt, T, H, D, GA, limite, kid, g_stream);
     return atencao_tras(g_blk, (const int8_t*)gom, (const int8_t*)goE, (const int8_t*)qm, (const int8_t*)qE, (const uint8_t*)P, (int*)Gacc,
                         (int16_t*)Ge, Bt, T, H, D, GA, limite, kid, g_stream);
+}
+int jt_atencao_via(int via) {
+    if (via < 0 || via > 1) return (int)cudaErrorInvalidValue;
+    g_at_via = via;
+    return 0;
 }
 
 // Attention backward for callers that must not allocate device memory: a process that runs under a fixed memory

@@ -52,3 +52,15 @@ def test_retomar_continua_bit_a_bit():
         b.passo(*dados.lote(fonte, gb, 2, 32), k_lr=4)
     for i, (x, y) in enumerate(zip(_estado(a), _estado(b))):
         assert torch.equal(x, y), f"state tensor {i} differs after resume"
+
+
+def test_corpus_no_dispositivo_corta_os_mesmos_lotes():
+    """The device-resident corpus draws the windows of the plain loader (same generator, same batches)."""
+    from jatai_b200 import dados
+    fonte = dados.sintetico(3000, 4)
+    c = dados.Corpus(fonte)
+    ga, gb = torch.Generator().manual_seed(5), torch.Generator().manual_seed(5)
+    for _ in range(3):
+        xa, ya = dados.lote(fonte, ga, 3, 24)
+        xb, yb = c.lote(gb, 3, 24)
+        assert xb.dtype == torch.long and torch.equal(xa, xb) and torch.equal(ya, yb)

@@ -92,11 +92,9 @@ GEMMS = [(n, b, f) for n, b, f in casos.tabela(32) + casos.tabela(128) if "/gemm
 @pytest.mark.parametrize("via", [1, 2, 3])
 @pytest.mark.parametrize("nome,blk,f", GEMMS, ids=[n for n, _, _ in GEMMS])
 def test_gemm_vias(amb, nome, blk, f, via):
-    """via 1 = tensor core with FFMA rounding (block 32 only; not valid for saturated mantissas), 2 = CUDA cores,
-    3 = tensor core with cvt rounding."""
+    """via 1 = tensor core forced (block 32: FMA rounding with its range check, which the saturated-mantissa case sends to the
+    conversion; block 128: conversion), 2 = CUDA cores, 3 = tensor core with the conversion everywhere."""
     ops, oc, reg = amb
-    if via == 1 and (blk != 32 or "limite" in nome):
-        pytest.skip("FFMA rounding is defined for block 32 and partial products below 2^18")
     ops.define_blk(blk)
     assert oc.lib.jt_gemm_via(via) == 0
     try:
@@ -382,3 +380,68 @@ def test_rms_back_soma_junto(amb, blk, M, D):
         compara(f"rms_back_soma {M}x{D} blk {blk} (vs specification)", casos.plano(junto), casos.plano(spec.Spec(blk).rms_back_soma(res, g, y, cache)))
     finally:
         ops.define_blk(32)
+
+
+@pytest.mark.parametrize("tn", [64, 128])
+@pytest.mark.parametrize("caso", ["tudo +127", "sinais alternados", "uma linha saturada", "um bloco saturado por linha"])
+def test_gemm_produtos_parciais_grandes(amb, caso, tn):
+    """Partial products at and above 2^18 with no alignment shift (s = 0): the inputs on which rounding by an FMA against
+    1.5*2^23 would leave its exact range.  The kernel must find them (a range check on the biased patterns) and round those
+    columns by conversion - in whole tiles, in single rows and in single K-blocks, for positive and negative products."""
+    ops, oc, reg = amb
+    ops.define_blk(32)
+    oc.lib.jt_gemm_via(0)
+    assert oc.lib.jt_gemm_tn(tn) == 0
+    try:
+        reg.novo_passo(0)
+        G = casos.Gen(8181, 32)
+        M, K, N = 256, 512, 256
+        A, B = G.bloco(M, K, espalha=0), G.bloco(N, K, espalha=0)
+        if caso == "tudo +127":
+            A, B = (torch.full_like(A[0], 127), A[1]), (torch.full_like(B[0], 127), B[1])
+        elif caso == "sinais alternados":            # every K-block of a row entirely +127 or -127: products of both signs at 32 * 127^2
+            sa = (torch.arange(K // 32) % 2 * 2 - 1).repeat_interleave(32).to(torch.int8)
+            A = ((127 * sa).expand(M, K).contiguous(), A[1])
+            B = (torch.where(torch.arange(N)[:, None] % 3 == 0, -127, 127).to(torch.int8).expand(N, K).contiguous(), B[1])
+        elif caso == "uma linha saturada":
+            A[0][37] = 127
+            B[0][101] = -127
+        else:                                         # one saturated K-block per row, at a different place in every row
+            for i in range(M):
+                b = i % (K // 32)
+                A[0][i, 32 * b:32 * b + 32] = 127 if i % 2 else -127
+            B = (torch.full_like(B[0], 127), B[1])
+        for cru in (False, True):
+            outs = casos.plano(oc.gemm(para_gpu(A), para_gpu(B), cru=cru))
+            torch.cuda.synchronize()
+            compara(f"gemm {caso} tn {tn} cru {cru}", outs, casos.plano(spec.Spec(32).gemm(A, B, cru=cru)))
+    finally:
+        oc.lib.jt_gemm_tn(0)
+
+
+@pytest.mark.parametrize("limite", [False, True])
+@pytest.mark.parametrize("blk,Bt,T,H,D", [(32, 2, 128, 2, 128), (32, 1, 160, 2, 128), (32, 2, 256, 8, 512), (128, 2, 64, 2, 128), (32, 1, 704, 1, 64)])
+def test_atencao_nucleos_tensor_e_cuda(amb, blk, Bt, T, H, D, limite):
+    """Head dimension 64 has two implementations - tensor cores (the default) and the CUDA-core kernels (jt_atencao_via(1),
+    also what the no-allocation entry point runs): forward and backward must agree bit for bit, on sequence lengths that
+    fill whole key chunks and on ones that do not."""
+    ops, oc, reg = amb
+    ops.define_blk(blk)
+    reg.novo_passo(0)
+    G = casos.Gen(7 * T + H + D + blk, blk)
+    M = Bt * T
+    qkv, go = para_gpu(G.bloco(M, 3 * D, espalha=6, zera=0.05)), para_gpu(G.bloco(M, D, e0=-20, espalha=6, zera=0.05))
+    ops.ATENCAO_LIMITE = limite
+    saidas = []
+    try:
+        for via in (0, 1):
+            assert oc.lib.jt_atencao_via(via) == 0
+            o, P = oc.atencao(qkv, Bt, T, H)
+            g = oc.atencao_back(go, qkv, P, Bt, T, H)
+            torch.cuda.synchronize()
+            saidas.append([*o, P, *g])
+    finally:
+        ops.ATENCAO_LIMITE = False
+        oc.lib.jt_atencao_via(0)
+        ops.define_blk(32)
+    compara(f"atencao tensor x cuda {blk}/{Bt}/{T}/{H}/{D} limite={limite}", saidas[0], saidas[1])
