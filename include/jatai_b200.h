@@ -97,7 +97,15 @@ int jt_blk_atual(void);
  * 3 tensor cores with every K-block rounded by a float-to-int conversion (block 32's default rounds with an FMA against
  * 1.5*2^23 after a range check, and converts only the columns that fail it; both are exact for every input). */
 int jt_gemm_via(int via);
-/* Attention path: 0 automatic (tensor cores when the head dimension is 64) | 1 CUDA-core kernels.  Same bits either way. */
+/* jt_quant(jt_atencao(...)) / jt_quant(jt_atencao_back(...)) with the quantisation done in the attention kernels' output stage:
+ * Om, OE = block tensor [Bt*T, D]; Gm, GE = block tensor [Bt*T, 3D] (gq | gk | gv); other arguments as in jt_atencao /
+ * jt_atencao_back.  Same results as the two calls.  Served at block length 32, head dimension 64, T >= 128 (the tensor-core
+ * path); cudaErrorNotSupported (801) elsewhere - compose the two calls then. */
+int jt_atencao_quant(const void* qm, const void* qE, void* Om, void* OE, void* P, int Bt, int T, int H, int D, int GA, int kid);
+int jt_atencao_back_quant(const void* gom, const void* goE, const void* qm, const void* qE, const void* P, void* Gm, void* GE,
+                          int Bt, int T, int H, int D, int GA, int limite, int kid);
+/* Attention path: 0 automatic (tensor cores when the head dimension is 64 and T >= 128; one CTA per head when T <= 128 and the
+ * head dimension is 4 or 16) | 1 the tiled CUDA-core kernels.  Same bits either way. */
 int jt_atencao_via(int via);
 /* Tile width of the tensor-core GEMM: 0 automatic (64 columns when 128-column tiles would leave most SMs idle, block
  * 32 only) | 64 | 128. */

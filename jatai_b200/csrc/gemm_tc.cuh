@@ -82,7 +82,10 @@ __device__ __forceinline__ bool espera(uint32_t bar, uint32_t par, volatile int*
         if ((it & 255) == 0) {
             const long long agora = clock64();
             if (t0 == 0) t0 = agora;
-            else if (agora - t0 > LIMITE_CICLOS) {
+            else if (*reinterpret_cast<volatile int*>(&g_erro.codigo) == E_TEMPO && *reinterpret_cast<volatile int*>(&g_erro.n) != 0) {
+                *aborta = 1;                     // a wait has already expired somewhere in this step: do not wait out another limit
+                return false;
+            } else if (agora - t0 > LIMITE_CICLOS) {
                 *aborta = 1;
                 reporta(E_TEMPO, kid, onde, par, blockIdx.x + 65536LL * blockIdx.y);
                 return false;
@@ -130,6 +133,15 @@ __device__ __forceinline__ void tmem_le16x2(uint32_t ta, uint32_t tb, uint32_t (
         "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%33];\n"
         "tcgen05.wait::ld.sync.aligned;\n"
         : JT_O16(a, 0), JT_O16(b, 0)
+        : "r"(ta), "r"(tb)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_le8x2(uint32_t ta, uint32_t tb, uint32_t (&a)[8], uint32_t (&b)[8]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%16];\n"
+        "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%8,%9,%10,%11,%12,%13,%14,%15}, [%17];\n"
+        "tcgen05.wait::ld.sync.aligned;\n"
+        : JT_O4(a, 0), JT_O4(a, 4), JT_O4(b, 0), JT_O4(b, 4)
         : "r"(ta), "r"(tb)
         : "memory");
 }
@@ -364,35 +376,35 @@ __global__ void __launch_bounds__(Cfg<TNv>::N_THR, Cfg<TNv>::CTAS_SM) k_gemm_tc(
                     const uint64_t fa0p = par_f(fa0, fa0), fa1p = par_f(fa1, fa1);
                     const uint64_t cn0p = par_f(-VIES_F * fa0, -VIES_F * fa0), cn1p = par_f(-VIES_F * fa1, -VIES_F * fa1);
 #pragma unroll
-                    for (int hf = 0; hf < 2; hf++) {
-                        uint32_t d0[16], d1[16];
-                        const uint32_t base = tmem + ((uint32_t)(quarto * 32) << 16) + cg * 32 + hf * 16;
-                        tmem_le16x2(base + t0 * TNv, base + t1 * TNv, d0, d1);
-                        if (hf == 1) {
+                    for (int hf = 0; hf < 4; hf++) {                   // 8 columns of two slices at a time
+                        uint32_t d0[8], d1[8];
+                        const uint32_t base = tmem + ((uint32_t)(quarto * 32) << 16) + cg * 32 + hf * 8;
+                        tmem_le8x2(base + t0 * TNv, base + t1 * TNv, d0, d1);
+                        if (hf == 3) {
                             tc_fence_antes();
                             __syncwarp();
                             if (lane == 0) { mbar_arrive(bar_tempty + 8 * t0); mbar_arrive(bar_tempty + 8 * t1); }
                         }
                         uint32_t o0 = 0, o1 = 0;
 #pragma unroll
-                        for (int k = 0; k < 16; k += 2) {
+                        for (int k = 0; k < 8; k += 2) {
                             d0[k] += VIES; d0[k + 1] += VIES; d1[k] += VIES; d1[k + 1] += VIES;
                             o0 |= d0[k] | d0[k + 1];
                             o1 |= d1[k] | d1[k + 1];
                         }
                         const bool largo = (sa0 == 0 && (o0 & 0xFFF80000u) != MAGIA) || (sa1 == 0 && (o1 & 0xFFF80000u) != MAGIA);
-                        const float* tb0 = tabB + (sl * 4 + t0) * TNv + cg * 32 + hf * 16;
+                        const float* tb0 = tabB + (sl * 4 + t0) * TNv + cg * 32 + hf * 8;
                         const float* tb1 = tb0 + TNv;
                         if (__any_sync(FULL, largo)) {
                             // some |p| >= 2^18 in a slice this row takes unshifted: the conversion rounds every magnitude
 #pragma unroll
-                            for (int k = 0; k < 16; k++) {
+                            for (int k = 0; k < 8; k++) {
                                 const float g0 = fmaf(__uint_as_float(d0[k]), fa0, -VIES_F * fa0), g1 = fmaf(__uint_as_float(d1[k]), fa1, -VIES_F * fa1);
-                                acc[hf * 16 + k] += __float2int_rn(g0 * tb0[k]) + __float2int_rn(g1 * tb1[k]) + (int)(2u * MAGIA);
+                                acc[hf * 8 + k] += __float2int_rn(g0 * tb0[k]) + __float2int_rn(g1 * tb1[k]) + (int)(2u * MAGIA);
                             }
                         } else {
 #pragma unroll
-                            for (int k4 = 0; k4 < 4; k4++) {
+                            for (int k4 = 0; k4 < 2; k4++) {
                                 const ulonglong2 b0 = reinterpret_cast<const ulonglong2*>(tb0)[k4], b1 = reinterpret_cast<const ulonglong2*>(tb1)[k4];
                                 const uint64_t fb0[2] = {b0.x, b0.y}, fb1[2] = {b1.x, b1.y};
 #pragma unroll
@@ -403,8 +415,8 @@ __global__ void __launch_bounds__(Cfg<TNv>::N_THR, Cfg<TNv>::CTAS_SM) k_gemm_tc(
                                     uint32_t x0, y0, x1, y1;
                                     separa(r0, x0, y0);
                                     separa(r1, x1, y1);
-                                    acc[hf * 16 + k] += (int)(x0 + x1);
-                                    acc[hf * 16 + k + 1] += (int)(y0 + y1);
+                                    acc[hf * 8 + k] += (int)(x0 + x1);
+                                    acc[hf * 8 + k + 1] += (int)(y0 + y1);
                                 }
                             }
                         }

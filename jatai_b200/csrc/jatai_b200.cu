@@ -20,6 +20,7 @@
 #include "gemm_tc.cuh"
 #include "atencao.cuh"
 #include "atencao_tc.cuh"
+#include "atencao_peq.cuh"
 
 using namespace jt;
 
@@ -28,7 +29,7 @@ static cudaStream_t g_stream = 0;
 static int g_blk = 32;               // exponent block length: 32 (native) or 128 (the reference's format)
 static int g_via = 0;                // GEMM path: 0 automatic | 1 tensor core (forced) | 2 CUDA cores | 3 tensor core, rounding by conversion
 static int g_alvo_ctas = 148;
-static int g_at_via = 0;             // attention path: 0 automatic (tensor cores at head dimension 64) | 1 CUDA cores
+static int g_at_via = 0;             // attention path: 0 automatic (tensor cores at head dimension 64, one CTA per head for short sequences of small heads) | 1 the tiled CUDA-core kernels
 static int g_tn = 0;                 // tile width of the tensor-core GEMM: 0 automatic | 64 | 128        // split-K of raw GEMMs aims at this many CTAs
 
 static int fim() { return (int)cudaGetLastError(); }
@@ -332,16 +333,34 @@ int jt_softmax_ce(const void* acc, const void* e, const void* alvo, void* gm, vo
 // ---------------------------------------------------------------------------------------------- attention
 int jt_atencao(const void* qm, const void* qE, void* Oacc, void* Oe, void* P, int Bt, int T, int H, int D, int GA, int kid) {
     if (g_at_via == 0 && Bt > 0 && H > 0 && atc_serve(g_blk, T, H, D))
-        return atencao_frente_tc(g_blk, (const int8_t*)qm, (const int8_t*)qE, (int*)Oacc, (int16_t*)Oe, (uint8_t*)P, Bt, T, H, D, GA, kid, g_stream);
+        return atencao_frente_tc(g_blk, (const int8_t*)qm, (const int8_t*)qE, (int*)Oacc, (int16_t*)Oe, nullptr, nullptr, (uint8_t*)P, Bt, T, H, D, GA, kid, g_stream);
+    if (g_at_via == 0 && Bt > 0 && atp_serve(g_blk, T, H, D))
+        return atencao_frente_peq(g_blk, (const int8_t*)qm, (const int8_t*)qE, (int*)Oacc, (int16_t*)Oe, (uint8_t*)P, Bt, T, H, D, GA, kid, g_stream);
     return atencao_frente(g_blk, (const int8_t*)qm, (const int8_t*)qE, (int*)Oacc, (int16_t*)Oe, (uint8_t*)P, Bt, T, H, D, GA, kid, g_stream);
 }
 int jt_atencao_back(const void* gom, const void* goE, const void* qm, const void* qE, const void* P, void* Gacc, void* Ge, int Bt, int T,
                     int H, int D, int GA, int limite, int kid) {
     if (g_at_via == 0 && Bt > 0 && H > 0 && atc_serve(g_blk, T, H, D))
         return atencao_tras_tc(g_blk, (const int8_t*)gom, (const int8_t*)goE, (const int8_t*)qm, (const int8_t*)qE, (const uint8_t*)P, (int*)Gacc,
-                               (int16_t*)Ge, Bt, T, H, D, GA, limite, kid, g_stream);
+                               (int16_t*)Ge, nullptr, nullptr, Bt, T, H, D, GA, limite, kid, g_stream);
+    if (g_at_via == 0 && Bt > 0 && atp_serve(g_blk, T, H, D))
+        return atencao_tras_peq(g_blk, (const int8_t*)gom, (const int8_t*)goE, (const int8_t*)qm, (const int8_t*)qE, (const uint8_t*)P, (int*)Gacc,
+                                (int16_t*)Ge, Bt, T, H, D, GA, limite, kid, g_stream);
     return atencao_tras(g_blk, (const int8_t*)gom, (const int8_t*)goE, (const int8_t*)qm, (const int8_t*)qE, (const uint8_t*)P, (int*)Gacc,
                         (int16_t*)Ge, Bt, T, H, D, GA, limite, kid, g_stream);
+}
+// jt_quant(jt_atencao(...)) and jt_quant(jt_atencao_back(...)) in the attention kernels' own output stage: block tensors [Bt*T, D] and
+// [Bt*T, 3D] come out directly.  Served where the tensor-core path is (head dimension 64, T >= 128) at block length 32; elsewhere
+// cudaErrorNotSupported, and the caller composes the two operations.
+int jt_atencao_quant(const void* qm, const void* qE, void* Om, void* OE, void* P, int Bt, int T, int H, int D, int GA, int kid) {
+    if (g_at_via != 0 || g_blk != 32 || Bt <= 0 || H <= 0 || !atc_serve(g_blk, T, H, D)) return (int)cudaErrorNotSupported;
+    return atencao_frente_tc(g_blk, (const int8_t*)qm, (const int8_t*)qE, nullptr, nullptr, (int8_t*)Om, (int8_t*)OE, (uint8_t*)P, Bt, T, H, D, GA, kid, g_stream);
+}
+int jt_atencao_back_quant(const void* gom, const void* goE, const void* qm, const void* qE, const void* P, void* Gm, void* GE, int Bt, int T, int H,
+                          int D, int GA, int limite, int kid) {
+    if (g_at_via != 0 || g_blk != 32 || Bt <= 0 || H <= 0 || !atc_serve(g_blk, T, H, D)) return (int)cudaErrorNotSupported;
+    return atencao_tras_tc(g_blk, (const int8_t*)gom, (const int8_t*)goE, (const int8_t*)qm, (const int8_t*)qE, (const uint8_t*)P, nullptr, nullptr,
+                           (int8_t*)Gm, (int8_t*)GE, Bt, T, H, D, GA, limite, kid, g_stream);
 }
 int jt_atencao_via(int via) {
     if (via < 0 || via > 1) return (int)cudaErrorInvalidValue;

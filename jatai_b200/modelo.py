@@ -73,6 +73,20 @@ class Modelo:
             return junto(gx, gn, y, cache)
         return self.ops.soma(gx, self.ops.rms_back(gn, y, cache))
 
+    def _atencao_quant(self, qkv, Bt, T):
+        """quant(atencao(qkv)) and P: one launch where the operator object offers the pair."""
+        junto = getattr(self.ops, "atencao_quant", None)
+        if junto is not None:
+            return junto(qkv, Bt, T, self.H)
+        oc, P = self.ops.atencao(qkv, Bt, T, self.H)
+        return self.ops.quant(oc), P
+
+    def _atencao_back_quant(self, go, qkv, P, Bt, T):
+        junto = getattr(self.ops, "atencao_back_quant", None)
+        if junto is not None:
+            return junto(go, qkv, P, Bt, T, self.H)
+        return self.ops.quant(self.ops.atencao_back(go, qkv, P, Bt, T, self.H))
+
     def _transpoe_par(self, gy, x):
         """Both operands of a weight-gradient GEMM transposed: one launch where the operator object offers the pair."""
         par = getattr(self.ops, "transpoe2", None)
@@ -112,6 +126,29 @@ class Modelo:
                     self._adiados.append((nome, a, b, ops.max_linha(a), ops.max_linha(b)))
             finally:
                 ops.lib.jt_stream(principal.cuda_stream)
+
+    def _pesos_transpostos(self):
+        """The backward multiplies by every weight transposed (and re-quantised along the new rows).  The weights do not change
+        between the start of a step and their own update, so on the CUDA launcher all those transpositions are issued at the
+        start of the step on the second stream, beside the forward pass, instead of inside the backward's dependency chain.
+        Returns {id of the weight's mantissa tensor: transposed block tensor} (empty where there is no second stream)."""
+        if self._lado is None:
+            return {}
+        ops, principal = self.ops, torch.cuda.current_stream()
+        self._lado.wait_stream(principal)
+        wt = {}
+        with torch.cuda.stream(self._lado):
+            ops.lib.jt_stream(self._lado.cuda_stream)
+            try:
+                with self.reg.trecho("pesos transpostos"):
+                    for n, w in self.p.items():
+                        if n != "emb":
+                            wt[id(w[0])] = t = ops.transpoe(w)
+                            for x in t:
+                                x.record_stream(principal)
+            finally:
+                ops.lib.jt_stream(principal.cuda_stream)
+        return wt
 
     def _otimiza_pendente(self):
         """Single GPU, on the second stream: the optimiser step of the weight whose gradient was computed by the
@@ -185,6 +222,23 @@ class Modelo:
         """Forward and (if `treina`) backward.  Weight gradients land in self._grads (single GPU) or, data parallel,
         their operands in self._adiados.  No communication happens here.  With `k_lr` on a single GPU the optimiser
         step of each weight also runs here, on the second stream, as soon as its gradient exists."""
+        for _ in self.em_trechos(tok, alvo, treina=treina, k_lr=k_lr):
+            pass
+        return self._perda
+
+    def cortes(self, grupos):
+        """Layer indices after which the backward is cut so that it falls into `grupos` pieces of consecutive layers (the
+        backward walks the layers from the last to the first; the output head belongs to the first piece, the embedding to
+        the last)."""
+        ordem = list(reversed(range(self.L)))
+        grupos = max(1, min(grupos, self.L))
+        return {ordem[len(ordem) * g // grupos - 1] for g in range(1, grupos)}
+
+    def em_trechos(self, tok, alvo, treina=True, k_lr=None, cortes=()):
+        """`frente_tras` as a generator: it yields after the backward of every layer listed in `cortes`, with the side
+        stream joined, so that a caller can end a CUDA graph there and put a collective between two pieces (data
+        parallel: the weight-gradient operands of the piece just finished are the new entries of self._adiados).  The loss
+        tensor is left in self._perda."""
         ops, reg, p = self.ops, self.reg, self.p
         Bt, T = tok.shape
         tok = tok.reshape(-1).to(torch.int32).contiguous()
@@ -193,6 +247,7 @@ class Modelo:
         self._pendente, self._feitos = None, set()
         self._k_lr_lado = k_lr if (self.redutor is None and self._lado is not None) else None
         guardados = []
+        wt = self._pesos_transpostos() if treina else {}
         with reg.trecho("forward"):
             with reg.trecho("embedding"):
                 x = ops.embed(p["emb"], tok)
@@ -201,8 +256,7 @@ class Modelo:
                     with reg.trecho("atencao"):
                         n1, c1 = ops.rms(x)
                         qkv = ops.gemm(n1, p[f"Wqkv{l}"])
-                        oc, P = ops.atencao(qkv, Bt, T, self.H)
-                        om = ops.quant(oc)
+                        om, P = self._atencao_quant(qkv, Bt, T)
                         x = ops.gemm_soma(om, p[f"Wo{l}"], x)
                         self._st(f"c{l}.qkv", qkv); self._st(f"c{l}.atencao_saida", om); self._st(f"c{l}.residuo1", x)
                     with reg.trecho("mlp"):
@@ -219,10 +273,12 @@ class Modelo:
                 else:
                     g, d_alvo, soma = ops.softmax_ce(logits, alvo, log2M=self.redutor.log2_tokens(tok.numel()))
         # loss report: stays on the device; the caller converts after the step without stalling the queue
-        perda = (d_alvo.double() / 256 + torch.log(soma.double() / 4096)).mean()
+        self._perda = perda = (d_alvo.double() / 256 + torch.log(soma.double() / 4096)).mean()
         if not treina:
-            return perda
-        T_ = ops.transpoe
+            return
+        if self._lado is not None and wt:
+            torch.cuda.current_stream().wait_stream(self._lado)         # the transposed weights are ready (they were, long ago)
+        T_ = lambda w: wt[id(w[0])] if id(w[0]) in wt else ops.transpoe(w)
         with reg.trecho("backward"):
             with reg.trecho("saida"):
                 self._grad_peso("out", g, nf)
@@ -241,11 +297,15 @@ class Modelo:
                     with reg.trecho("atencao"):
                         self._grad_peso(f"Wo{l}", gx, om)
                         go = ops.gemm(gx, T_(p[f"Wo{l}"]))
-                        gq = ops.quant(ops.atencao_back(go, qkv, P, Bt, T, self.H))
+                        gq = self._atencao_back_quant(go, qkv, P, Bt, T)
                         self._grad_peso(f"Wqkv{l}", gq, n1)
                         gn = ops.gemm(gq, T_(p[f"Wqkv{l}"]))
                         gx = self._soma_rms_back(gx, gn, n1, c1)
                         self._st(f"c{l}.grad_qkv", gq); self._st(f"c{l}.grad_residuo", gx)
+                if l in cortes:
+                    if self._lado is not None:
+                        torch.cuda.current_stream().wait_stream(self._lado)
+                    yield l
             with reg.trecho("embedding"):
                 self._grad_peso("emb", ops.um_quente(tok, self.V), gx)
         if self._lado is not None:
@@ -259,7 +319,6 @@ class Modelo:
                     finally:
                         ops.lib.jt_stream(principal.cuda_stream)
             torch.cuda.current_stream().wait_stream(self._lado)          # join the weight-gradient branch
-        return perda
 
 
 class PassoGravado:
@@ -270,13 +329,23 @@ class PassoGravado:
     the graph stays valid.  Inputs go to fixed buffers (copy_) before each replay.  The launch list of the
     recording is kept: the launch ids are baked into the kernel arguments, so a sentinel raised during a replay
     names the same operation and section as it would in eager mode.  Run one eager step before recording (the
-    attention backward sizes its workspace on first use, which a capture does not allow).  Data parallel: the
-    step is recorded as 1 + 2 GRUPOS graphs (forward+backward | per group of weights: deferred weight-gradient GEMMs
-    | optimiser) and the collectives run eagerly between the replays: one MAX for the whole step, then one SUM per
-    group, which overlaps the next group's GEMMs while the group's optimiser step follows on a second stream.
+    attention sizes its workspace on first use, which a capture does not allow).
+
+    Data parallel: no collective is ever part of a captured graph; the step is cut into GRUPOS pieces of consecutive layers
+    and recorded as 3 graphs per piece, with the collectives issued eagerly between the replays:
+        M_g  forward (g = 0) and the backward of piece g, the transpositions and row maxima of its weight-gradient operands
+             on the side branch, the maxima packed into their slice of the flat buffer                      main stream
+        MAX  all-reduce of that slice (a few KB, on a communicator of its own)
+        D_g  the weight-gradient GEMMs of piece g with the global maxima, sums packed into the flat buffer   second stream
+        SUM  all-reduce of the piece's int32 sums (asynchronous)
+        O_g  the optimiser step of the piece's weights                                                      second stream
+    The main stream goes straight on to M_{g+1} after queueing MAX_g, so the weight-gradient GEMMs, the gradient traffic and
+    the optimiser of piece g run beside the backward of piece g + 1, as the single-GPU step runs them beside its backward;
+    only the last piece's tail is exposed.  The backward never reads a weight again after its own piece (it multiplies by
+    the transposed copies made at the start of the step), so O_g may update it while the backward goes on.
     """
 
-    GRUPOS = 4          # data parallel: pieces the weight-gradient tail (GEMMs | SUM collective | optimiser) is pipelined in
+    GRUPOS = 4          # data parallel: pieces of consecutive layers
 
     def __init__(self, modelo, Bt, T, k_lr):
         self.m, self.reg, self.k_lr = modelo, modelo.reg, k_lr
@@ -295,53 +364,59 @@ class PassoGravado:
                     lib.jt_stream(torch.cuda.current_stream().cuda_stream)
                     self.perda = modelo.passo(self.tok, self.alvo, k_lr=k_lr)
             else:
-                # Data parallel: three graphs with the two collectives issued eagerly between them, so that no
-                # collective is ever part of a captured graph.  The reducer's flat buffers must already exist with
-                # their final sizes (one eager step has run), so the graphs see fixed addresses.
+                # The reducer's flat buffers must already exist with their final sizes (one eager step has run), so the
+                # graphs see fixed addresses.
                 assert getattr(red, "_max", None) is not None and getattr(red, "_plano", None) is not None, \
                     "run one eager data-parallel step before recording"
-                g0 = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g0):
-                    lib.jt_stream(torch.cuda.current_stream().cuda_stream)
-                    self.perda = modelo.frente_tras(self.tok, self.alvo)
-                    pares = [(ra, rb) for _, _, _, ra, rb in modelo._adiados]
-                    red.empacota_maximos(pares)
-                # The tail is cut into groups of consecutive weights: while group g's sums cross the wire, group
-                # g+1's GEMMs run, and group g's optimiser step runs on a second stream as soon as its sums are in.
-                # The GEMM graphs share graph 0's pool (replayed in recording order on one stream); the optimiser
-                # graphs have a pool of their own (they run beside the GEMM graphs).
-                n = len(pares)
-                ng = min(self.GRUPOS, n)
-                cortes = [n * g // ng for g in range(ng + 1)]
-                maximos = red.vistas_maximos(pares)
-                nomes = [a[0] for a in modelo._adiados]
-                self._gemm, self._otim, self._fatias, vistas_g = [], [], [], []
+                cortes = modelo.cortes(self.GRUPOS)
+                ng = len(cortes) + 1
+                trechos = modelo.em_trechos(self.tok, self.alvo, treina=True, k_lr=None, cortes=cortes)
+                self._M, self._D, self._O, self._fatias_max, self._fatias = [], [], [], [], []
+                grupos, n0, o_max, pool_m = [], 0, 0, None
                 for g in range(ng):
-                    gg = torch.cuda.CUDAGraph()
-                    with torch.cuda.graph(gg, pool=g0.pool()):
+                    gm = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(gm, **({} if pool_m is None else {"pool": pool_m})):
                         lib.jt_stream(torch.cuda.current_stream().cuda_stream)
-                        modelo._gemms_adiados(maximos, cortes[g], cortes[g + 1])
-                        v, fatia = red.empacota_grupo({k: modelo._grads[k] for k in nomes[cortes[g]:cortes[g + 1]]}, modelo._grads)
-                    self._gemm.append(gg)
-                    self._fatias.append(fatia)
-                    vistas_g.append(v)
-                self._vivos = (vistas_g, dict(modelo._grads))        # keeps every tensor the graphs read at its address
+                        next(trechos, None)
+                        novos = modelo._adiados[n0:]
+                        o1 = red.empacota_maximos([(ra, rb) for _, _, _, ra, rb in novos], o_max)
+                    pool_m = gm.pool()
+                    self._M.append(gm)
+                    self._fatias_max.append((o_max, o1))
+                    grupos.append((n0, n0 + len(novos)))
+                    n0, o_max = n0 + len(novos), o1
+                assert next(trechos, "fim") == "fim" and o_max == red._max.numel()
+                self.perda = modelo._perda
+                adiados = list(modelo._adiados)                       # every operand the later graphs read stays referenced here
+                maximos = red.vistas_maximos([(ra, rb) for _, _, _, ra, rb in adiados])
+                nomes = [a[0] for a in adiados]
                 self._lado = torch.cuda.Stream(device=modelo.dev)
-                pool_o = None
-                for g in range(ng):
-                    go = torch.cuda.CUDAGraph()
-                    with torch.cuda.graph(go, **({} if pool_o is None else {"pool": pool_o})):
-                        lib.jt_stream(torch.cuda.current_stream().cuda_stream)
-                        with self.reg.trecho("otimizador"):
-                            modelo._otimiza(vistas_g[g], k_lr)
-                    pool_o = go.pool()
-                    self._otim.append(go)
-                self.grafos = [g0] + self._gemm + self._otim
+                pool_l, vistas_g = None, []
+                with torch.cuda.stream(self._lado):
+                    for g, (a0, a1) in enumerate(grupos):
+                        gd = torch.cuda.CUDAGraph()
+                        with torch.cuda.graph(gd, stream=self._lado, **({} if pool_l is None else {"pool": pool_l})):
+                            lib.jt_stream(torch.cuda.current_stream().cuda_stream)
+                            modelo._adiados = adiados
+                            modelo._gemms_adiados(maximos, a0, a1)
+                            v, fatia = red.empacota_grupo({k: modelo._grads[k] for k in nomes[a0:a1]}, modelo._grads)
+                        pool_l = gd.pool()
+                        go = torch.cuda.CUDAGraph()
+                        with torch.cuda.graph(go, stream=self._lado, pool=pool_l):
+                            lib.jt_stream(torch.cuda.current_stream().cuda_stream)
+                            with self.reg.trecho("otimizador"):
+                                modelo._otimiza(v, k_lr)
+                        self._D.append(gd)
+                        self._O.append(go)
+                        self._fatias.append(fatia)
+                        vistas_g.append(v)
+                self._vivos = (adiados, vistas_g, dict(modelo._grads), maximos)
+                self.grafos = self._M + self._D + self._O
         finally:
             lib.jt_stream(None)
             modelo.estatisticas, self.reg.vigiar, self.reg.perfil = est, vig, perf
         self.lancamentos = list(self.reg.lancamentos)
-        self.coletivos_por_passo = 0 if red is None else 1 + len(self._fatias)
+        self.coletivos_por_passo = 0 if red is None else 2 * len(self._M)
         self.reg.info(f"step recorded in {len(self.grafos)} CUDA graph(s): {len(self.lancamentos)} launches", lancamentos=len(self.lancamentos))
 
     def __call__(self, tok, alvo):
@@ -350,18 +425,17 @@ class PassoGravado:
         self.reg.lancamentos = self.lancamentos
         if len(self.grafos) == 1:
             self.grafos[0].replay()
-        else:
-            red = self.m.redutor
-            principal = torch.cuda.current_stream()
-            self.grafos[0].replay()
-            red.reduz_maximos()
-            for g, (gg, go, fatia) in enumerate(zip(self._gemm, self._otim, self._fatias)):
-                gg.replay()
-                pronto = red.reduz_fatia(*fatia)                  # asynchronous: ordered after this group's GEMMs
-                if g == 0:
-                    self._lado.wait_stream(principal)             # the optimiser may not overtake the backward's last read of a weight
-                with torch.cuda.stream(self._lado):
-                    pronto.wait()
-                    go.replay()
-            principal.wait_stream(self._lado)
+            return self.perda
+        red = self.m.redutor
+        principal = torch.cuda.current_stream()
+        for gm, gd, go, fmax, fsoma in zip(self._M, self._D, self._O, self._fatias_max, self._fatias):
+            gm.replay()
+            pronto_max = red.reduz_maximos_fatia(*fmax)           # asynchronous, ordered after the piece just queued
+            with torch.cuda.stream(self._lado):
+                pronto_max.wait()
+                gd.replay()
+                pronto = red.reduz_fatia(*fsoma)                  # asynchronous: ordered after this piece's GEMMs
+                pronto.wait()
+                go.replay()
+        principal.wait_stream(self._lado)                         # the next step reads every weight
         return self.perda

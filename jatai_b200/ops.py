@@ -31,7 +31,7 @@ BIBLIOTECA = os.path.join(AQUI, "libjatai_b200.so")
 _INT_FUNCS = ("jt_gemm", "jt_gemm_f", "jt_gemm_ext", "jt_max_linha", "jt_quant", "jt_soma", "jt_relu2", "jt_relu2_back",
               "jt_momento", "jt_peso", "jt_momento_peso", "jt_transpoe", "jt_transpoe2", "jt_embed", "jt_um_quente", "jt_rms", "jt_rms_back", "jt_rms_back_soma", "jt_atencao",
               "jt_atencao_back", "jt_softmax_ce", "jt_erro_le", "jt_erro_limpa", "jt_sincroniza", "jt_para16", "jt_para8",
-              "jt_soma16", "jt_res_estocastico", "jt_blk", "jt_blk_atual", "jt_gemm_via", "jt_gemm_tn", "jt_atencao_back_fixo", "jt_atencao_via")
+              "jt_soma16", "jt_res_estocastico", "jt_blk", "jt_blk_atual", "jt_gemm_via", "jt_gemm_tn", "jt_atencao_back_fixo", "jt_atencao_via", "jt_atencao_quant", "jt_atencao_back_quant")
 
 
 def g_rms(D):
@@ -97,7 +97,7 @@ class OpsCuda:
             raise RuntimeError("this library has a fixed block length of 128; call ops.define_blk(128) first")
         # a library with only the reference's entry points: the fused extras read as absent, callers fall back to the separate operations
         for metodo, fn in (("transpoe2", "jt_transpoe2"), ("momento_peso", "jt_momento_peso"), ("rms_back_soma", "jt_rms_back_soma"),
-                           ("max_linha", "jt_max_linha")):
+                           ("max_linha", "jt_max_linha"), ("atencao_quant", "jt_atencao_quant"), ("atencao_back_quant", "jt_atencao_back_quant")):
             if not hasattr(self.lib, fn):
                 setattr(self, metodo, None)
 
@@ -310,6 +310,37 @@ class OpsCuda:
         self._lanca("atencao_back", "jt_atencao_back", (gm, gE, m, E, P, acc, e), (Bt, T, H, D, GA, int(ATENCAO_LIMITE)),
                     dict(go=gm, goE=gE, qkv=m, qkvE=E, P=P), (Bt * T, 3 * D))
         return acc, e
+
+    def _atencao_fundida(self, T, H, D):
+        """Whether the library quantises the attention outputs in its own output stage for this shape (else: two launches)."""
+        return BLK == 32 and D == 64 * H and T % 64 == 0 and 128 <= T <= 1024
+
+    def atencao_quant(self, QKV, Bt, T, H):
+        """(quant(O), P) of atencao(QKV, Bt, T, H): one launch where the library offers it (an addition of this library; same results)."""
+        D = QKV[0].shape[1] // 3
+        if not self._atencao_fundida(T, H, D):
+            oc, P = self.atencao(QKV, Bt, T, H)
+            return self.quant(oc), P
+        self.reg.confere_bloco("qkv", QKV)
+        m, E = QKV
+        self.reg.exige(m.shape[0] == Bt * T, f"atencao_quant: rows {m.shape[0]} (= Bt*T = {Bt * T})")
+        O = self._bloco_vazio(Bt * T, D, m.device)
+        P = torch.empty(Bt * H, T, T, dtype=torch.uint8, device=m.device)
+        self._lanca("atencao_quant", "jt_atencao_quant", (m, E, O[0], O[1], P), (Bt, T, H, D, GA), dict(qkv=m, qkvE=E), (Bt * T, D))
+        return O, P
+
+    def atencao_back_quant(self, GO, QKV, P, Bt, T, H):
+        """quant(atencao_back(GO, QKV, P, Bt, T, H)): one launch sequence without the raw intermediate where the library offers it."""
+        D = GO[0].shape[1]
+        if not self._atencao_fundida(T, H, D):
+            return self.quant(self.atencao_back(GO, QKV, P, Bt, T, H))
+        self.reg.confere_bloco("go", GO)
+        self.reg.confere_bloco("qkv", QKV)
+        (gm, gE), (m, E) = GO, QKV
+        G = self._bloco_vazio(Bt * T, 3 * D, m.device)
+        self._lanca("atencao_back_quant", "jt_atencao_back_quant", (gm, gE, m, E, P, G[0], G[1]), (Bt, T, H, D, GA, int(ATENCAO_LIMITE)),
+                    dict(go=gm, goE=gE, qkv=m, qkvE=E, P=P), (Bt * T, 3 * D))
+        return G
 
     # ------------------------------------------------------------------ loss and optimiser
     def softmax_ce(self, L, alvo, log2M=None):

@@ -28,6 +28,8 @@ class Redutor:
         assert dist.is_initialized(), "initialise torch.distributed first"
         self.grupo = grupo
         self.mundo = dist.get_world_size(grupo)
+        # the small MAX exchanges get a communicator of their own, so that they never queue behind a gradient SUM in flight
+        self.grupo_max = dist.new_group(ranks=dist.get_process_group_ranks(grupo) if grupo is not None else None)
         self.bytes_max = 0        # bytes this rank put on the wire, per kind (for the bench report)
         self.bytes_soma = 0
         self.chamadas = 0
@@ -50,12 +52,13 @@ class Redutor:
         self.reduz_maximos()
         return self.vistas_maximos(pares)
 
-    def empacota_maximos(self, pares):
-        o = 0
+    def empacota_maximos(self, pares, o=0):
+        """Copies local maxima into the flat buffer from offset `o` on; returns the offset after them."""
         for ra, rb in pares:
             for r in (ra, rb):
                 self._max[o:o + r.numel()].copy_(r)
                 o += r.numel()
+        return o
 
     def vistas_maximos(self, pares):
         o, out = 0, []
@@ -67,9 +70,16 @@ class Redutor:
         return out
 
     def reduz_maximos(self):
-        dist.all_reduce(self._max, op=dist.ReduceOp.MAX, group=self.grupo)
+        dist.all_reduce(self._max, op=dist.ReduceOp.MAX, group=self.grupo_max)
         self.bytes_max += self._max.numel()
         self.chamadas += 1
+
+    def reduz_maximos_fatia(self, o0, o1):
+        """MAX over ranks of one slice of the flat buffer of maxima, asynchronously; returns the work handle."""
+        w = dist.all_reduce(self._max[o0:o1], op=dist.ReduceOp.MAX, group=self.grupo_max, async_op=True)
+        self.bytes_max += o1 - o0
+        self.chamadas += 1
+        return w
 
     def soma_tudo(self, grads):
         """Exact integer sum over ranks of every weight gradient of a step, as ONE collective: the int32 partial

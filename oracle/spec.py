@@ -177,6 +177,14 @@ class Spec:
         """soma(X, rms_back(Gg, Y, cache)) (the CUDA library offers the pair as one launch)."""
         return self.soma(X, self.rms_back(Gg, Y, cache))
 
+    def atencao_quant(self, QKV, Bt, T, H):
+        """(quant(O), P) of atencao (the CUDA library offers the pair without the raw intermediate)."""
+        oc, P = self.atencao(QKV, Bt, T, H)
+        return self.quant(oc), P
+
+    def atencao_back_quant(self, GO, QKV, P, Bt, T, H):
+        return self.quant(self.atencao_back(GO, QKV, P, Bt, T, H))
+
     def transpoe2(self, X1, X2):
         """Two transpositions (the CUDA library offers the pair as one launch)."""
         return self.transpoe(X1), self.transpoe(X2)

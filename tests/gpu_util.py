@@ -18,6 +18,11 @@ class ConferidoNaGpu:
         self.n = {}
 
     def _atencao_r(self, op, args):
+        if op == "atencao_quant":
+            o, P = self._atencao_r("atencao", args)
+            return self.r.quant(o), P
+        if op == "atencao_back_quant":
+            return self.r.quant(self._atencao_r("atencao_back", args))
         if op == "atencao":
             qkv, Bt, T, H = args
             partes = [self.r.atencao(tuple(t[b * T:(b + 1) * T].contiguous() for t in qkv), 1, T, H) for b in range(Bt)]
@@ -33,7 +38,7 @@ class ConferidoNaGpu:
 
         def f(*args, **kw):
             copia = [tuple(t.clone() for t in a) if isinstance(a, tuple) and op in ("momento", "peso", "momento_peso") else a for a in args]
-            if self.por_sequencia and op in ("atencao", "atencao_back"):
+            if self.por_sequencia and op in ("atencao", "atencao_back", "atencao_quant", "atencao_back_quant"):
                 out_r = self._atencao_r(op, copia)
             else:
                 out_r = fr(*copia, **kw)

@@ -31,7 +31,7 @@ def test_config5_dois_passos_conferidos():
         reg.fim_passo()
     assert all(3.0 < x < 8.0 for x in perdas), perdas
     n = m.ops.n
-    assert n["atencao"] == 4 and n["atencao_back"] == 4 and n["momento_peso"] == 2 * 10 and n["gemm"] >= 2 * (1 + 1 + 4 * 2 + 2 * 2)
+    assert n["atencao_quant"] == 4 and n["atencao_back_quant"] == 4 and n["momento_peso"] == 2 * 10 and n["gemm"] >= 2 * (1 + 1 + 4 * 2 + 2 * 2)
 
 
 def test_config5_grafo_igual_ao_eager_24_camadas():

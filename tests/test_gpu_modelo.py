@@ -43,7 +43,7 @@ def test_passo_conferido():
         reg.fim_passo()
         assert perda == perda and perda < 10
     n = m.ops.n
-    assert n["gemm"] >= 2 * (1 + 1 + 4 * CFG["L"] + CFG["L"] * 2) and n["atencao"] == 2 * CFG["L"] and n["momento_peso"] == 2 * (4 * CFG["L"] + 2)
+    assert n["gemm"] >= 2 * (1 + 1 + 4 * CFG["L"] + CFG["L"] * 2) and n["atencao_quant"] == 2 * CFG["L"] and n["momento_peso"] == 2 * (4 * CFG["L"] + 2)
 
 
 def test_grafo_igual_ao_eager():

@@ -212,7 +212,7 @@ def test_referencia_compat(amb):
 
 ATENCOES = [  # blk, Bt, T, H, D  (head dim D/H in {4, 16, 64}; T also off the 128 grid; block 128 with wide heads)
     (32, 2, 64, 4, 64), (32, 2, 128, 2, 128), (32, 1, 256, 8, 512), (32, 1, 160, 2, 128), (32, 2, 96, 16, 64),
-    (128, 2, 64, 2, 128), (128, 1, 192, 8, 128), (32, 1, 512, 2, 128),
+    (128, 2, 64, 2, 128), (128, 1, 192, 8, 128), (32, 1, 512, 2, 128), (32, 1, 192, 2, 128), (128, 1, 320, 2, 128), (32, 3, 128, 1, 64),
 ]
 
 
@@ -420,11 +420,12 @@ def test_gemm_produtos_parciais_grandes(amb, caso, tn):
 
 
 @pytest.mark.parametrize("limite", [False, True])
-@pytest.mark.parametrize("blk,Bt,T,H,D", [(32, 2, 128, 2, 128), (32, 1, 160, 2, 128), (32, 2, 256, 8, 512), (128, 2, 64, 2, 128), (32, 1, 704, 1, 64)])
+@pytest.mark.parametrize("blk,Bt,T,H,D", [(32, 2, 128, 2, 128), (32, 1, 192, 2, 128), (32, 1, 160, 2, 128), (32, 2, 256, 8, 512), (128, 2, 128, 2, 128),
+                                         (32, 1, 704, 1, 64), (32, 1, 320, 3, 192)])
 def test_atencao_nucleos_tensor_e_cuda(amb, blk, Bt, T, H, D, limite):
     """Head dimension 64 has two implementations - tensor cores (the default) and the CUDA-core kernels (jt_atencao_via(1),
-    also what the no-allocation entry point runs): forward and backward must agree bit for bit, on sequence lengths that
-    fill whole key chunks and on ones that do not."""
+    also what the no-allocation entry point runs, and what sequence lengths that are no multiple of 64 get): forward and backward
+    must agree bit for bit, on sequence lengths that fill whole key chunks and on ones that do not."""
     ops, oc, reg = amb
     ops.define_blk(blk)
     reg.novo_passo(0)
@@ -445,3 +446,30 @@ def test_atencao_nucleos_tensor_e_cuda(amb, blk, Bt, T, H, D, limite):
         oc.lib.jt_atencao_via(0)
         ops.define_blk(32)
     compara(f"atencao tensor x cuda {blk}/{Bt}/{T}/{H}/{D} limite={limite}", saidas[0], saidas[1])
+
+
+@pytest.mark.parametrize("limite", [False, True])
+@pytest.mark.parametrize("Bt,T,H,D", [(2, 128, 2, 128), (1, 256, 8, 512), (1, 192, 2, 128), (1, 1024, 1, 64)])
+def test_atencao_com_quant_fundido(amb, Bt, T, H, D, limite):
+    """The attention kernels that write their outputs already quantised (block length 32, head dimension 64) against
+    quant(atencao(...)) / quant(atencao_back(...)) of the specification, including rows whose block of 32 columns is entirely
+    zero and key tiles that end beyond T."""
+    ops, oc, reg = amb
+    ops.define_blk(32)
+    reg.novo_passo(0)
+    G = casos.Gen(11 * T + H + D, 32)
+    M = Bt * T
+    qkv, go = G.bloco(M, 3 * D, espalha=5, zera=0.1), G.bloco(M, D, e0=-20, espalha=6, zera=0.1)
+    s = spec.Spec(32, limite=limite)
+    o_r, P_r = s.atencao_quant(qkv, Bt, T, H)
+    g_r = s.atencao_back_quant(go, qkv, P_r, Bt, T, H)
+    ops.ATENCAO_LIMITE = limite
+    try:
+        o_c, P_c = oc.atencao_quant(para_gpu(qkv), Bt, T, H)
+        g_c = oc.atencao_back_quant(para_gpu(go), para_gpu(qkv), P_c, Bt, T, H)
+        torch.cuda.synchronize()
+    finally:
+        ops.ATENCAO_LIMITE = False
+    assert reg.lancamentos[-1]["op"] == "atencao_back_quant"          # the fused entry point ran, not the composition
+    compara(f"atencao_quant {Bt}/{T}/{H}/{D}", [*o_c, P_c], [*o_r, P_r])
+    compara(f"atencao_back_quant {Bt}/{T}/{H}/{D} limite={limite}", list(g_c), list(g_r))

@@ -138,4 +138,4 @@ def test_config4_tres_passos_conferidos(amb):
         perdas.append(float(m.passo(x[:, :-1].contiguous().cuda(), x[:, 1:].contiguous().cuda(), k_lr=4)))
         reg.fim_passo()
     assert all(p == p and 3.0 < p < 7.0 for p in perdas), perdas
-    assert m.ops.n["gemm"] >= 3 * 49 and m.ops.n["atencao_back"] == 36
+    assert m.ops.n["gemm"] >= 3 * 49 and m.ops.n["atencao_back_quant"] == 36
