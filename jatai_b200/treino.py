@@ -161,9 +161,20 @@ def velocidade(a, Bt, n=30):
     s.reg.novo_passo(0)
     s.grava(4)
     t_grafo = taxa(False)
-    s.reg.info(f"batch {Bt} x {a.T} = {Bt * a.T} tokens | INT8 CUDA {t_eager:,.0f} tokens/s eager, {t_grafo:,.0f} with a CUDA graph",
-               int8=t_eager, int8_grafo=t_grafo)
-    return t_eager, t_grafo
+    # the float32 yard-stick: the same model in plain PyTorch, from the same weights, same batches
+    from . import regua
+    pf = regua.PassoFloat(s.m, 4)
+    pf(*lotes[0])
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for i in range(n):
+        pf(*lotes[1 + i % 5])
+    torch.cuda.synchronize()
+    t_f32 = Bt * a.T * n / (time.perf_counter() - t0)
+    s.reg.info(f"batch {Bt} x {a.T} = {Bt * a.T} tokens | INT8 CUDA {t_eager:,.0f} tokens/s eager, {t_grafo:,.0f} with a CUDA graph | "
+               f"float32 PyTorch {t_f32:,.0f} tokens/s | INT8 / float32 = {t_eager / t_f32:.2f}x ({t_grafo / t_f32:.2f}x with the graph)",
+               int8=t_eager, int8_grafo=t_grafo, f32=t_f32)
+    return t_eager, t_grafo, t_f32
 
 
 def main(argv=None):

@@ -73,3 +73,18 @@ def test_dp_duas_ranks_igual_a_um_processo():
         for i, (a, b) in enumerate(zip(d["estado"], ref)):
             assert torch.equal(a, b), f"rank {r}: state tensor {i} differs from the single-process run"
         assert all(abs(a - b) < 1e-9 for a, b in zip(d["perdas"], perdas))
+
+
+def test_regua_float_acompanha_o_modelo_inteiro():
+    """The float32 yard-stick starts from the integer model's weights: its loss at initialisation is the integer model's
+    (up to the integer rounding), and one of its SGD steps lowers it on a repeated batch."""
+    from jatai_b200 import regua
+    m = _modelo()
+    tok, alvo = _lote(1)
+    p_int = float(m.passo(tok, alvo))
+    pf = regua.PassoFloat(m, 4)
+    p_f = float(pf.m(tok, alvo))
+    assert abs(p_f - p_int) < 0.05, (p_f, p_int)
+    for _ in range(3):
+        pf(tok, alvo)
+    assert float(pf.m(tok, alvo)) < p_f
