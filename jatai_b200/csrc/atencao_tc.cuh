@@ -219,7 +219,8 @@ __global__ void __launch_bounds__(NTL) k_atencao_tc(const __grid_constant__ CUte
                                                     int16_t* __restrict__ Oe, int8_t* __restrict__ Qm, int8_t* __restrict__ QE, uint8_t* __restrict__ P,
                                                     int T, int H, int D, int GA, int kid) {
     extern __shared__ unsigned char bruto[];
-    unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)bruto + 1023) & ~(uintptr_t)1023);
+    // (pointer arithmetic on the array keeps the shared address space: a round trip through an integer makes every access generic)
+    unsigned char* smem = bruto + ((1024u - (smem_u32(bruto) & 1023u)) & 1023u);
     const uint32_t sbase = smem_u32(smem);
     const int nchT = (T + TJ - 1) / TJ, TPX = T + 8;
     // 3 operand stages (a TMA load takes longer than one step of a sweep: loads run three steps ahead) | stacked query tile |
@@ -426,7 +427,8 @@ template <int FASE>
 __global__ void __launch_bounds__(NTL) k_ab_linhas_tc(const __grid_constant__ CUtensorMap mV, const __grid_constant__ CUtensorMap mG,
                                                       const __grid_constant__ CUtensorMap mKt, const ArgsTrasTC A) {
     extern __shared__ unsigned char bruto[];
-    unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)bruto + 1023) & ~(uintptr_t)1023);
+    // (pointer arithmetic on the array keeps the shared address space: a round trip through an integer makes every access generic)
+    unsigned char* smem = bruto + ((1024u - (smem_u32(bruto) & 1023u)) & 1023u);
     const uint32_t sbase = smem_u32(smem);
     // stages: V chunks [4] (a TMA load takes longer than a step of a sweep: loads run four steps ahead) | dO tile as loaded |
     // dO tile stacked | (phase 3) K^T chunks [4] | dS' digit tiles [2][hi rows, lo rows]
@@ -640,7 +642,8 @@ __global__ void __launch_bounds__(256) k_ab_colunas_tc(const __grid_constant__ C
                                                        const __grid_constant__ CUtensorMap mDh, const __grid_constant__ CUtensorMap mDl,
                                                        const __grid_constant__ CUtensorMap mP, const ArgsTrasTC A) {
     extern __shared__ unsigned char bruto[];
-    unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)bruto + 1023) & ~(uintptr_t)1023);
+    // (pointer arithmetic on the array keeps the shared address space: a round trip through an integer makes every access generic)
+    unsigned char* smem = bruto + ((1024u - (smem_u32(bruto) & 1023u)) & 1023u);
     const uint32_t sbase = smem_u32(smem);
     constexpr int NSTC = 3;                                        // a TMA load takes longer than a step: loads run two steps ahead
     constexpr uint32_t STAGE = 2 * TILE_A + 3 * TILE_NJ, OFF_BAR = NSTC * STAGE;

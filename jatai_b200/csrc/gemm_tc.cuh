@@ -182,7 +182,8 @@ __global__ void __launch_bounds__(Cfg<TNv>::N_THR, Cfg<TNv>::CTAS_SM) k_gemm_tc(
                        OFF_BAR = C_::OFF_BAR, OFF_MISC = C_::OFF_MISC, IDESC = C_::IDESC;
     static_assert(TNv == 128 || (TNv == 64 && BLK == 32), "64-column tiles exist for block 32 only");
     extern __shared__ unsigned char smem_bruto[];
-    unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_bruto + 1023) & ~(uintptr_t)1023);
+    // (pointer arithmetic on the array keeps the shared address space: a round trip through an integer makes every access generic)
+    unsigned char* smem = smem_bruto + ((1024u - (smem_u32(smem_bruto) & 1023u)) & 1023u);
     const uint32_t sbase = smem_u32(smem);
     int* acc_s = reinterpret_cast<int*>(smem + OFF_ACC);
     float* tabB = reinterpret_cast<float*>(smem + OFF_TAB);          // [NTB][4][TN]
