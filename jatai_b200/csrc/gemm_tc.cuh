@@ -29,7 +29,7 @@ constexpr int TM = 128, KC = 128, NST = 4, NTM = 4, NTB = 4;
 constexpr uint32_t A_BYTES = TM * KC;
 // everything that depends on the tile width TNv (columns of C per CTA): 128, or 64 for shapes whose 128-wide tiling
 // would leave most SMs without a CTA (block 32 only: a 128-column exponent block does not fit a 64-column tile)
-template <int TNv>
+template <int TNv, int VIA>
 struct Cfg {
     static constexpr int N_DW = TNv / 8;                       // drain warps: 4 lane quarters x (TNv / 32) column groups
     static constexpr int N_EPI = N_DW * 32, N_THR = 64 + N_EPI, PITCHv = TNv + 4;
@@ -45,7 +45,8 @@ struct Cfg {
     static constexpr uint32_t OFF_RBM = OFF_RBF + TNv * 4;                  // minimum and maximum RB of each block: int[4] + int[4]
     static constexpr uint32_t OFF_BAR = OFF_RBM + 32;
     static constexpr uint32_t OFF_MISC = OFF_BAR + (2 * NST + 2 * NTM + 2 * NTB) * 8;
-    static constexpr uint32_t SMEM_BYTES = OFF_MISC + 16 + 1024;            // + slack to align the base to 1024 bytes
+    static constexpr uint32_t OFF_C127 = (OFF_MISC + 16 + 1023) / 1024 * 1024;   // 1 KB of the byte 127: the constant operand
+    static constexpr uint32_t SMEM_BYTES = OFF_C127 + 1024 + 1024;          // + slack to align the base to 1024 bytes
     // 64-column tiles: two CTAs per SM (2 x 256 columns of tensor memory, 2 x ~100 KB of shared memory, <= 102 registers):
     // the prologue and the output stage of one overlap the main loop of the other
     static constexpr int CTAS_SM = TNv == 64 ? 2 : 1;
@@ -55,6 +56,7 @@ struct Cfg {
 constexpr long long LIMITE_CICLOS = 4000000000LL;              // ~2 s at B200 clocks
 constexpr uint32_t MAGIA = 0x4B400000u;                        // bit pattern of 1.5 * 2^23
 constexpr float MAGIA_F = 12582912.0f;
+constexpr int DESLOC = 32 * 127 * 127;                         // the largest |partial product| of 32 int8 pairs
 
 // ------------------------------------------------------------------------------------------ PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -162,22 +164,28 @@ __device__ __forceinline__ uint64_t ffma2(uint64_t a, uint64_t b, uint64_t c) {
 __device__ __forceinline__ float pot2(int e) { return __int_as_float((127 + e) << 23); }      // 2^e, -126 <= e <= 127
 
 // How a K-block's partial product p (exact int32 from tensor memory, |p| <= 32 * 127^2 < 2^19) becomes rnd(p << 4, sa + sb):
-// VIA 1 (block 32): p is biased into a float by an integer add of the pattern of 1.5*2^23 + 2^18, one FMA removes the bias and
-//        scales by 2^(4-sa) (exact), a second FMA against 1.5*2^23 scales by 2^-sb and rounds half to even in its single
-//        rounding; the result's bit pattern is added to the accumulator (the pattern of the constant times the slice count comes
-//        off at the end).  Two slices are drained together so that one three-input add serves both, and the FMAs are the packed
-//        two-lane form.  The rounding is exact while |p * 2^(4-s)| < 2^22, i.e. always except s = 0 with |p| >= 2^18; that case is
-//        found by OR-ing the biased patterns (bits 19.. differ from the constant's exactly when |p| >= 2^18; this is what the extra
-//        2^18 in the bias is for) and the 16 columns at hand are then rounded by VIA 2's conversion, for the whole warp.
+// VIA 1 (block 32): every slice gets a second MMA of two constant operands (all bytes 127) onto the same accumulator, so what
+//        the drain reads is p' = p + 32*127^2 >= 0.  Read as a float, the bit pattern of a non-negative integer below 2^23 is the
+//        subnormal p' * 2^-149 - an exact int -> float conversion that costs no instruction.  One FMA scales it by 2^(123-sa) and
+//        takes the constant off (exact: the result is (p' - 32*127^2) * 2^(-26-sa)), a second FMA against 1.5*2^23 scales by
+//        2^(30-sb) and rounds half to even in its single rounding; the result's bit pattern is added to the accumulator (the
+//        pattern of 1.5*2^23 times the slice count comes off at the end).  Two slices are drained together so that one three-input
+//        add serves both, and the FMAs are the packed two-lane form.  The rounding is exact while |p * 2^(4-s)| < 2^22, i.e.
+//        always except s = 0 with |p| >= 2^18, and exactly then the sum leaves [2^23, 2^24]: its exponent field changes.  The bit
+//        patterns of a half chunk's results are OR-ed as they are added, and a warp in which some pattern's top nine bits are not
+//        those of 1.5*2^23 reads the half chunk again (the stages are handed back only after this vote), takes the fast results
+//        off and adds VIA 2's conversions instead.
 // VIA 2: exact float product, cvt.rni to int (valid for every input; block 128, where four MMAs accumulate before a drain).
 template <int BLK, int MODO, int VIA, int TNv>
-__global__ void __launch_bounds__(Cfg<TNv>::N_THR, Cfg<TNv>::CTAS_SM) k_gemm_tc(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
+__global__ void __launch_bounds__(Cfg<TNv, VIA>::N_THR, Cfg<TNv, VIA>::CTAS_SM) k_gemm_tc(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                                                       const int8_t* __restrict__ EA, const int8_t* __restrict__ EB,
                                                       const int8_t* __restrict__ RAg, const int8_t* __restrict__ RBg, SaidaGemm S, int M, int N,
                                                       int K, int pedacos_por_parte, int kid) {
     constexpr int NQ = KC / BLK;                 // K-blocks per 128-byte chunk: 4 (BLK 32) or 1 (BLK 128)
-    using C_ = Cfg<TNv>;
+    using C_ = Cfg<TNv, VIA>;
     constexpr int N_DW = C_::N_DW, N_EPI = C_::N_EPI, PITCHv = C_::PITCHv;
+    constexpr bool PARES = BLK == 32 && VIA == 1;
+    static_assert(VIA != 1 || BLK == 32, "the FMA rounding is written for one MMA per drain");
     constexpr uint32_t STAGE_BYTES = C_::STAGE_BYTES, OFF_ACC = C_::OFF_ACC, OFF_TAB = C_::OFF_TAB, OFF_RA = C_::OFF_RA, OFF_RB = C_::OFF_RB, OFF_RBF = C_::OFF_RBF, OFF_RBM = C_::OFF_RBM,
                        OFF_BAR = C_::OFF_BAR, OFF_MISC = C_::OFF_MISC, IDESC = C_::IDESC;
     static_assert(TNv == 128 || (TNv == 64 && BLK == 32), "64-column tiles exist for block 32 only");
@@ -208,6 +216,10 @@ __global__ void __launch_bounds__(Cfg<TNv>::N_THR, Cfg<TNv>::CTAS_SM) k_gemm_tc(
         for (int i = 0; i < NTB; i++) { mbar_init(bar_bfull + 8 * i, 32); mbar_init(bar_bempty + 8 * i, N_DW); }
         *aborta = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (PARES) {
+        if (tid < 64) reinterpret_cast<uint4*>(smem + C_::OFF_C127)[tid] = make_uint4(0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");          // the MMA reads it through the async proxy
     }
     if (tid < TM) RAs[tid] = -128;
     if (tid < TNv) RBs[tid] = -128;
@@ -266,7 +278,7 @@ __global__ void __launch_bounds__(Cfg<TNv>::N_THR, Cfg<TNv>::CTAS_SM) k_gemm_tc(
 #pragma unroll
                 for (int q = 0; q < NQ; q++) {
                     const int sb = min(RBc[k] - (int)(int8_t)(w[k] >> (8 * q)), 40);
-                    tabB[(sl * 4 + q) * TNv + lane + 32 * k] = pot2(-sb);
+                    tabB[(sl * 4 + q) * TNv + lane + 32 * k] = pot2((PARES ? 30 : 0) - sb);
                 }
             mbar_arrive(bar_bfull + 8 * sl);
             if (i + 1 < pedacos_por_parte) le_w(i + 1);
@@ -276,6 +288,7 @@ __global__ void __launch_bounds__(Cfg<TNv>::N_THR, Cfg<TNv>::CTAS_SM) k_gemm_tc(
         if (lane == 0) {
             int f = 0;
             bool ok = true;
+            const uint64_t d127 = desc_sw128(sbase + C_::OFF_C127) & ~((uint64_t)0x3FFF << 32);
             for (int i = 0; i < pedacos_por_parte && ok; i++) {
                 const int s = i % NST;
                 if (!espera(bar_full + 8 * s, (i / NST) & 1, aborta, kid, 2)) break;
@@ -287,7 +300,10 @@ __global__ void __launch_bounds__(Cfg<TNv>::N_THR, Cfg<TNv>::CTAS_SM) k_gemm_tc(
                         const int t = f % NTM;
                         if (!espera(bar_tempty + 8 * t, ((f / NTM) & 1) ^ 1, aborta, kid, 3)) { ok = false; break; }
                         tc_fence_depois();
-                        tc_mma_i8(tmem + t * TNv, da + 2 * q, db + 2 * q, IDESC, 0);          // +32 bytes of K per instruction
+                        // VIA 1: the constant product 32 * 127 * 127 first (every 8-row group of both operands is the same 1 KB of
+                        // the byte 127: group stride 0), the slice's products on top of it
+                        if (VIA == 1) tc_mma_i8(tmem + t * TNv, d127, d127, IDESC, 0);
+                        tc_mma_i8(tmem + t * TNv, da + 2 * q, db + 2 * q, IDESC, VIA == 1 ? 1 : 0);      // +32 bytes of K per instruction
                         tc_commit(bar_tfull + 8 * t);
                     }
                 } else {
@@ -355,11 +371,8 @@ __global__ void __launch_bounds__(Cfg<TNv>::N_THR, Cfg<TNv>::CTAS_SM) k_gemm_tc(
         for (int j = 0; j < 32; j++) acc[j] = 0;
         int f = 0;
         bool ok = true;
-        constexpr bool PARES = BLK == 32 && VIA == 1;
         if constexpr (PARES) {
             static_assert(NQ == NTM, "one tensor-memory stage per K-block of a chunk");
-            constexpr uint32_t VIES = MAGIA + (1u << 18);                 // pattern of 1.5*2^23 + 2^18
-            constexpr float VIES_F = MAGIA_F + 262144.0f;
             const uint64_t magia2 = par_f(MAGIA_F, MAGIA_F);
             for (int c = 0; c < pedacos_por_parte && ok; c++) {
                 const int sl = c % NTB;
@@ -373,55 +386,62 @@ __global__ void __launch_bounds__(Cfg<TNv>::N_THR, Cfg<TNv>::CTAS_SM) k_gemm_tc(
                     if (!ok) break;
                     tc_fence_depois();
                     const int sa0 = min(RA - (int)(int8_t)(eaw >> (16 * h)), 40), sa1 = min(RA - (int)(int8_t)(eaw >> (16 * h + 8)), 40);
-                    const float fa0 = pot2(GG - sa0), fa1 = pot2(GG - sa1);
-                    const uint64_t fa0p = par_f(fa0, fa0), fa1p = par_f(fa1, fa1);
-                    const uint64_t cn0p = par_f(-VIES_F * fa0, -VIES_F * fa0), cn1p = par_f(-VIES_F * fa1, -VIES_F * fa1);
+                    const uint32_t base_h = tmem + ((uint32_t)(quarto * 32) << 16) + cg * 32;
+                    const float* tb_h = tabB + (sl * 4 + t0) * TNv + cg * 32;
+                    const float fa0 = pot2(123 - sa0), fa1 = pot2(123 - sa1);
+                    const float cn0 = -(float)DESLOC * pot2(GG - 30 - sa0), cn1 = -(float)DESLOC * pot2(GG - 30 - sa1);
+                    const uint64_t fa0p = par_f(fa0, fa0), fa1p = par_f(fa1, fa1), cn0p = par_f(cn0, cn0), cn1p = par_f(cn1, cn1);
+                    uint32_t ou = 0;
 #pragma unroll
                     for (int hf = 0; hf < 4; hf++) {                   // 8 columns of two slices at a time
-                        uint32_t d0[8], d1[8];
-                        const uint32_t base = tmem + ((uint32_t)(quarto * 32) << 16) + cg * 32 + hf * 8;
-                        tmem_le8x2(base + t0 * TNv, base + t1 * TNv, d0, d1);
-                        if (hf == 3) {
-                            tc_fence_antes();
-                            __syncwarp();
-                            if (lane == 0) { mbar_arrive(bar_tempty + 8 * t0); mbar_arrive(bar_tempty + 8 * t1); }
-                        }
-                        uint32_t o0 = 0, o1 = 0;
-#pragma unroll
-                        for (int k = 0; k < 8; k += 2) {
-                            d0[k] += VIES; d0[k + 1] += VIES; d1[k] += VIES; d1[k + 1] += VIES;
-                            o0 |= d0[k] | d0[k + 1];
-                            o1 |= d1[k] | d1[k + 1];
-                        }
-                        const bool largo = (sa0 == 0 && (o0 & 0xFFF80000u) != MAGIA) || (sa1 == 0 && (o1 & 0xFFF80000u) != MAGIA);
-                        const float* tb0 = tabB + (sl * 4 + t0) * TNv + cg * 32 + hf * 8;
+                        uint32_t d0[8], d1[8];                         // p' = p + 32*127^2: as floats, the subnormals p' * 2^-149
+                        tmem_le8x2(base_h + hf * 8 + t0 * TNv, base_h + hf * 8 + t1 * TNv, d0, d1);
+                        const float* tb0 = tb_h + hf * 8;
                         const float* tb1 = tb0 + TNv;
-                        if (__any_sync(FULL, largo)) {
-                            // some |p| >= 2^18 in a slice this row takes unshifted: the conversion rounds every magnitude
 #pragma unroll
-                            for (int k = 0; k < 8; k++) {
-                                const float g0 = fmaf(__uint_as_float(d0[k]), fa0, -VIES_F * fa0), g1 = fmaf(__uint_as_float(d1[k]), fa1, -VIES_F * fa1);
-                                acc[hf * 8 + k] += __float2int_rn(g0 * tb0[k]) + __float2int_rn(g1 * tb1[k]) + (int)(2u * MAGIA);
-                            }
-                        } else {
+                        for (int k4 = 0; k4 < 2; k4++) {
+                            const ulonglong2 b0 = reinterpret_cast<const ulonglong2*>(tb0)[k4], b1 = reinterpret_cast<const ulonglong2*>(tb1)[k4];
+                            const uint64_t fb0[2] = {b0.x, b0.y}, fb1[2] = {b1.x, b1.y};
 #pragma unroll
-                            for (int k4 = 0; k4 < 2; k4++) {
-                                const ulonglong2 b0 = reinterpret_cast<const ulonglong2*>(tb0)[k4], b1 = reinterpret_cast<const ulonglong2*>(tb1)[k4];
-                                const uint64_t fb0[2] = {b0.x, b0.y}, fb1[2] = {b1.x, b1.y};
-#pragma unroll
-                                for (int k2 = 0; k2 < 2; k2++) {
-                                    const int k = 4 * k4 + 2 * k2;
-                                    const uint64_t r0 = ffma2(ffma2(par(d0[k], d0[k + 1]), fa0p, cn0p), fb0[k2], magia2);
-                                    const uint64_t r1 = ffma2(ffma2(par(d1[k], d1[k + 1]), fa1p, cn1p), fb1[k2], magia2);
-                                    uint32_t x0, y0, x1, y1;
-                                    separa(r0, x0, y0);
-                                    separa(r1, x1, y1);
-                                    acc[hf * 8 + k] += (int)(x0 + x1);
-                                    acc[hf * 8 + k + 1] += (int)(y0 + y1);
-                                }
+                            for (int k2 = 0; k2 < 2; k2++) {
+                                const int k = 4 * k4 + 2 * k2;
+                                const uint64_t r0 = ffma2(ffma2(par(d0[k], d0[k + 1]), fa0p, cn0p), fb0[k2], magia2);
+                                const uint64_t r1 = ffma2(ffma2(par(d1[k], d1[k + 1]), fa1p, cn1p), fb1[k2], magia2);
+                                uint32_t x0, y0, x1, y1;
+                                separa(r0, x0, y0);
+                                separa(r1, x1, y1);
+                                ou |= x0 | y0;
+                                ou |= x1 | y1;
+                                acc[hf * 8 + k] += (int)(x0 + x1);
+                                acc[hf * 8 + k + 1] += (int)(y0 + y1);
                             }
                         }
                     }
+                    if (__any_sync(FULL, (ou & 0xFF800000u) != (MAGIA & 0xFF800000u))) {
+                        // some result left the window of the rounding constant: take the fast results off again, add the conversions
+                        const float ga0 = pot2(GG - 30 - sa0), ga1 = pot2(GG - 30 - sa1);
+#pragma unroll 1
+                        for (int hf = 0; hf < 4; hf++) {
+                            uint32_t d0[8], d1[8];
+                            tmem_le8x2(base_h + hf * 8 + t0 * TNv, base_h + hf * 8 + t1 * TNv, d0, d1);
+                            const float* tb0 = tb_h + hf * 8;
+                            const float* tb1 = tb0 + TNv;
+#pragma unroll
+                            for (int k = 0; k < 8; k++) {
+                                const float f0 = tb0[k], f1 = tb1[k];
+                                const uint32_t rap0 = __float_as_uint(fmaf(fmaf(__uint_as_float(d0[k]), fa0, cn0), f0, MAGIA_F));
+                                const uint32_t rap1 = __float_as_uint(fmaf(fmaf(__uint_as_float(d1[k]), fa1, cn1), f1, MAGIA_F));
+                                const int ex0 = __float2int_rn(((float)((int)d0[k] - DESLOC) * ga0) * f0), ex1 = __float2int_rn(((float)((int)d1[k] - DESLOC) * ga1) * f1);
+                                const int dif = (int)((uint32_t)ex0 + MAGIA - rap0) + (int)((uint32_t)ex1 + MAGIA - rap1);
+                                // the accumulator is a compile-time register only under full unrolling: select by hf
+#pragma unroll
+                                for (int g = 0; g < 4; g++) acc[g * 8 + k] += g == hf ? dif : 0;
+                            }
+                        }
+                    }
+                    tc_fence_antes();
+                    __syncwarp();
+                    if (lane == 0) { mbar_arrive(bar_tempty + 8 * t0); mbar_arrive(bar_tempty + 8 * t1); }
                 }
                 if (!ok) break;
                 __syncwarp();

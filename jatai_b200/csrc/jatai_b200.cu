@@ -40,7 +40,7 @@ template <int BLK, int MODO, int VIA, int TNv>
 static int lanca_tc(const CUtensorMap& mA, const CUtensorMap& mB, const int8_t* EA, const int8_t* EB, const int8_t* RA, const int8_t* RB,
                     const SaidaGemm& S, int M, int N, int K, int partes, int kid) {
     static bool feito[64];                 // kernel attributes are per device
-    using C_ = tc::Cfg<TNv>;
+    using C_ = tc::Cfg<TNv, VIA>;
     auto k = tc::k_gemm_tc<BLK, MODO, VIA, TNv>;
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return (int)cudaErrorInvalidDevice;
