@@ -294,16 +294,28 @@ __global__ void __launch_bounds__(Cfg<TNv, VIA>::N_THR, Cfg<TNv, VIA>::CTAS_SM) 
                 if (!espera(bar_full + 8 * s, (i / NST) & 1, aborta, kid, 2)) break;
                 tc_fence_depois();
                 const uint64_t da = desc_sw128(sbase + s * STAGE_BYTES), db = desc_sw128(sbase + s * STAGE_BYTES + A_BYTES);
-                if (BLK == 32) {
+                if (BLK == 32 && VIA == 1) {
+                    // two slices per hand-over (the drain takes them together): barriers of the even stages only.  The constant
+                    // product 32 * 127 * 127 goes in first (every 8-row group of both operands is the same 1 KB of the byte 127:
+                    // group stride 0), the slices' products on top of it.
+#pragma unroll
+                    for (int q = 0; q < 4; q += 2, f += 2) {
+                        const int t = f % NTM;
+                        if (!espera(bar_tempty + 8 * t, ((f / NTM) & 1) ^ 1, aborta, kid, 3)) { ok = false; break; }
+                        tc_fence_depois();
+                        tc_mma_i8(tmem + t * TNv, d127, d127, IDESC, 0);
+                        tc_mma_i8(tmem + (t + 1) * TNv, d127, d127, IDESC, 0);
+                        tc_mma_i8(tmem + t * TNv, da + 2 * q, db + 2 * q, IDESC, 1);               // +32 bytes of K per instruction
+                        tc_mma_i8(tmem + (t + 1) * TNv, da + 2 * q + 2, db + 2 * q + 2, IDESC, 1);
+                        tc_commit(bar_tfull + 8 * t);
+                    }
+                } else if (BLK == 32) {
 #pragma unroll
                     for (int q = 0; q < 4; q++, f++) {
                         const int t = f % NTM;
                         if (!espera(bar_tempty + 8 * t, ((f / NTM) & 1) ^ 1, aborta, kid, 3)) { ok = false; break; }
                         tc_fence_depois();
-                        // VIA 1: the constant product 32 * 127 * 127 first (every 8-row group of both operands is the same 1 KB of
-                        // the byte 127: group stride 0), the slice's products on top of it
-                        if (VIA == 1) tc_mma_i8(tmem + t * TNv, d127, d127, IDESC, 0);
-                        tc_mma_i8(tmem + t * TNv, da + 2 * q, db + 2 * q, IDESC, VIA == 1 ? 1 : 0);      // +32 bytes of K per instruction
+                        tc_mma_i8(tmem + t * TNv, da + 2 * q, db + 2 * q, IDESC, 0);               // +32 bytes of K per instruction
                         tc_commit(bar_tfull + 8 * t);
                     }
                 } else {
@@ -382,7 +394,7 @@ __global__ void __launch_bounds__(Cfg<TNv, VIA>::N_THR, Cfg<TNv, VIA>::CTAS_SM) 
 #pragma unroll
                 for (int h = 0; h < 2; h++) {
                     const int t0 = 2 * h, t1 = 2 * h + 1;
-                    ok = __all_sync(FULL, espera(bar_tfull + 8 * t0, c & 1, aborta, kid, 4) && espera(bar_tfull + 8 * t1, c & 1, aborta, kid, 4));
+                    ok = __all_sync(FULL, espera(bar_tfull + 8 * t0, c & 1, aborta, kid, 4));      // one hand-over for both stages
                     if (!ok) break;
                     tc_fence_depois();
                     const int sa0 = min(RA - (int)(int8_t)(eaw >> (16 * h)), 40), sa1 = min(RA - (int)(int8_t)(eaw >> (16 * h + 8)), 40);
@@ -441,7 +453,7 @@ __global__ void __launch_bounds__(Cfg<TNv, VIA>::N_THR, Cfg<TNv, VIA>::CTAS_SM) 
                     }
                     tc_fence_antes();
                     __syncwarp();
-                    if (lane == 0) { mbar_arrive(bar_tempty + 8 * t0); mbar_arrive(bar_tempty + 8 * t1); }
+                    if (lane == 0) mbar_arrive(bar_tempty + 8 * t0);
                 }
                 if (!ok) break;
                 __syncwarp();
