@@ -398,9 +398,11 @@ template <int TR, int CPT>
 __device__ __forceinline__ void transpoe32_corpo(const int8_t* __restrict__ X, const int8_t* __restrict__ EX, int8_t* __restrict__ Y,
                                                  int8_t* __restrict__ EY, int R, int C, int kid) {
     static_assert(CPT == 4 || CPT == 1, "a thread owns the 4 columns of a word or one of them");
-    constexpr int TC = 256, PW = T32_PW, NT = 8 * TR / CPT;
+    constexpr int TC = 256, PW = T32_PW, NT = 8 * TR / CPT, NPAR = (TR / 32) * 8;
     __shared__ uint32_t tile[TR][PW];
     __shared__ __align__(4) int8_t et[TR][8];
+    __shared__ float fA[TR][8];                   // 2^(e - largest exponent of the row's 32-row block), per 32-column block
+    __shared__ int eref_s[NPAR];                  // that largest exponent; bit 30 set: exponents too far apart for fp32
     const int r0 = blockIdx.y * TR, c0 = blockIdx.x * TC;
     const int tid = threadIdx.x;
     const int nbx = C / 32, nby = R / 32;
@@ -415,21 +417,23 @@ __device__ __forceinline__ void transpoe32_corpo(const int8_t* __restrict__ X, c
         *reinterpret_cast<uint32_t*>(&et[lr][k4]) = *reinterpret_cast<const uint32_t*>(EX + (size_t)(r0 + lr) * nbx + c0 / 32 + k4);
     }
     __syncthreads();
+    // scales of the rows: a warp per (32-row block, 32-column block), a lane per row.  Rows of all-zero blocks do not count
+    // for the spread (their mantissas are zero whatever the scale).
+    for (int p = tid >> 5; p < NPAR; p += NT / 32) {
+        const int rb = p >> 3, cb = p & 7, i = tid & 31;
+        const int e = et[rb * 32 + i][cb];
+        const int eref = __reduce_max_sync(0xffffffffu, e);
+        const int emin = __reduce_min_sync(0xffffffffu, e == E_ZERO ? 127 : e);
+        fA[rb * 32 + i][cb] = __int_as_float(max(127 + e - eref, 0) << 23);
+        if (i == 0) eref_s[p] = (eref & 0xffff) | (eref - emin > 100 ? 1 << 30 : 0);
+    }
+    __syncthreads();
     // word column, 32-row block and (CPT = 1: small matrices, four times the threads) the byte of the word
     const int cw = tid & 63, rb = CPT == 4 ? tid >> 6 : tid >> 8, k_meu = (tid >> 6) & 3;
-    uint32_t w[32];
-    float A[32];
-    int eref = -128, emin = 127;
-#pragma unroll
-    for (int i = 0; i < 32; i++) {
-        w[i] = tile[rb * 32 + i][cw];
-        const int e = et[rb * 32 + i][cw >> 3];
-        eref = max(eref, e);
-        if (w[i]) emin = min(emin, e);
-    }
-#pragma unroll
-    for (int i = 0; i < 32; i++) A[i] = __int_as_float(max(127 + (int)et[rb * 32 + i][cw >> 3] - eref, 0) << 23);
-    const bool largo = eref - emin > 100;                           // spread too wide for the fp32 path
+    const int er = eref_s[rb * 8 + (cw >> 3)];
+    const int eref = (int)(int16_t)(er & 0xffff);
+    const bool largo = (er >> 30) & 1;                              // spread too wide for the fp32 path
+    const float* fa = &fA[rb * 32][cw >> 3];
 #pragma unroll
     for (int k = 0; k < 4; k++) {
         if (CPT == 1 && k != k_meu) continue;
@@ -443,7 +447,7 @@ __device__ __forceinline__ void transpoe32_corpo(const int8_t* __restrict__ X, c
         float t[32], mx = 0.f;
 #pragma unroll
         for (int i = 0; i < 32; i++) {
-            t[i] = (float)(int)(int8_t)(w[i] >> (8 * k)) * A[i];
+            t[i] = (float)(int)(int8_t)(tile[rb * 32 + i][cw] >> (8 * k)) * fa[8 * i];     // the words stay in shared memory: registers hold t
             mx = fmaxf(mx, fabsf(t[i]));
         }
         const int expo = (__float_as_int(mx) >> 23) - 127;          // floor(log2 mx); mx is a normal number or 0 here
@@ -467,7 +471,7 @@ __device__ __forceinline__ void transpoe32_corpo(const int8_t* __restrict__ X, c
 }
 
 template <int TR, int CPT = 4>
-__global__ void __launch_bounds__(8 * TR / CPT, 512 / (8 * TR / CPT)) k_transpoe32(const int8_t* __restrict__ X, const int8_t* __restrict__ EX,
+__global__ void __launch_bounds__(8 * TR / CPT, 768 / (8 * TR / CPT)) k_transpoe32(const int8_t* __restrict__ X, const int8_t* __restrict__ EX,
                                                                                    int8_t* __restrict__ Y, int8_t* __restrict__ EY, int R, int C,
                                                                                    int kid) {
     transpoe32_corpo<TR, CPT>(X, EX, Y, EY, R, C, kid);
@@ -477,7 +481,7 @@ __global__ void __launch_bounds__(8 * TR / CPT, 512 / (8 * TR / CPT)) k_transpoe
 // GEMM): blockIdx.z picks the matrix, the grid is as wide as the wider one.
 struct ArgsTransp { const int8_t* X; const int8_t* EX; int8_t* Y; int8_t* EY; int C; };
 template <int TR, int CPT = 4>
-__global__ void __launch_bounds__(8 * TR / CPT, 512 / (8 * TR / CPT)) k_transpoe32_par(ArgsTransp a0, ArgsTransp a1, int R, int kid) {
+__global__ void __launch_bounds__(8 * TR / CPT, 768 / (8 * TR / CPT)) k_transpoe32_par(ArgsTransp a0, ArgsTransp a1, int R, int kid) {
     const ArgsTransp a = blockIdx.z ? a1 : a0;
     if ((int)blockIdx.x * 256 >= a.C) return;
     transpoe32_corpo<TR, CPT>(a.X, a.EX, a.Y, a.EY, R, a.C, kid);
