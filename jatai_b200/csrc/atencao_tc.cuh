@@ -304,7 +304,36 @@ __global__ void __launch_bounds__(NTL) k_atencao_tc(const __grid_constant__ CUte
             const int j = c * TJ + jl;
             uint32_t hh[16], cr[16], ll[16];
             tmem_le16x3(t_lane + st * SB + 16 * g, hh, cr, ll);
-            if (j < nproc) {
+            if (j < nproc && s_u > 0 && s_u < 31) {
+                // the usual case, a right shift: rounding, slope and exponential written out with their invariants hoisted.
+                //   rnd_d(x, s)              = (x + 2^(s-1) - 1 + ((x >> s) & 1)) >> s
+                //   exp_int(d) >> 3, d>=0    : t = min(d, 6000) * 23637, n = t >> 22, f = bits 7..21 of t; the cubic in f runs on
+                //                              p * 2^16 (|p| < 2^15 at every step): (p f) >> 15 = mulhi(p << 16, 2 f); the result
+                //                              p >> (n + 3) is 0 from n = 12 on (0 <= p < 2^15), as is the shift clamped to 31
+                const int meio = (1 << (s_u - 1)) - 1, dj = i0 + 16 * g - j, menos = -(1 << incl);
+                const bool diagonal = c == nch - 1;                    // the only chunk with keys beyond some query of the tile
+#pragma unroll
+                for (int k = 0; k < 16; k++) {
+                    const int x = junta3(hh[k], cr[k], ll[k]);
+                    int u = (x + meio + ((x >> s_u) & 1)) >> s_u;
+                    u += (dj + k) * menos;
+                    const bool dentro = !diagonal || dj + k >= 0;
+                    if (cc < nch) v16[k] = max(v16[k], dentro ? u : U_MIN);
+                    else {
+                        // a key beyond the diagonal counts as infinitely far below the maximum; mi >= u otherwise, and
+                        // |u| < 2^30 + 2^18: the difference cannot overflow
+                        const int t = min(dentro ? mi[k] - u : 6000, 6000) * 23637;
+                        const int f2 = (t >> 6) & 0xFFFE;
+                        int pp = -1295 * 65536;
+                        pp = __mulhi(pp, f2) * 65536 + 7556 * 65536;
+                        pp = __mulhi(pp, f2) * 65536 - 22645 * 65536;
+                        pp = __mulhi(pp, f2) * 65536 + 32765 * 65536;
+                        const int ex = pp >> min(19 + (t >> 22), 31);
+                        v16[k] += ex;
+                        ex_s[(16 * g + k) * TPX + j] = (uint16_t)ex;
+                    }
+                }
+            } else if (j < nproc) {
 #pragma unroll
                 for (int k = 0; k < 16; k++) {
                     const int i = i0 + 16 * g + k;
