@@ -28,6 +28,7 @@
 //
 // Every mbarrier wait is bounded (sentinel 7, abort flag, normal exit with tensor memory freed), as in the block GEMM.
 #pragma once
+#include <type_traits>
 #include "comum.cuh"
 #include "gemm_tc.cuh"
 #include "atencao.cuh"
@@ -567,28 +568,47 @@ __global__ void __launch_bounds__(NTL) k_ab_linhas_tc(const __grid_constant__ CU
                 pw[0] = w.x; pw[1] = w.y; pw[2] = w.z; pw[3] = w.w;
             }
             int dh[16], dl[16];
+            // A key counts for query i0 + 16 g + k when it exists for this tile (j < nproc) and is not beyond the diagonal, which only
+            // the last chunk can be: one comparison of k against a per-thread bound.  With both shifts in 1..30 the roundings are
+            // written out with their constants hoisted: rnd_d(x, s) = (x + 2^(s-1) - 1 + ((x >> s) & 1)) >> s.
+            const int kmin = j >= nproc ? 16 : (c == nch - 1 ? j - (i0 + 16 * g) : 0);      // dentro <=> k >= kmin
+            auto corpo = [&](auto rapido_t) {
+                constexpr bool RAP = decltype(rapido_t)::value;
+                const int meio1 = RAP && FASE != 1 ? (1 << max(sh - 1, 0)) - 1 : 0, meio2 = RAP && FASE == 3 ? (1 << max(sh2 - 1, 0)) - 1 : 0;
 #pragma unroll
-            for (int k = 0; k < 16; k++) {
-                const int i = i0 + 16 * g + k;
-                const bool dentro = j <= i && j < nproc;
-                const int gp = dentro ? rnd_d(junta3(hh[k], cr[k], ll[k]), sh) : 0;
-                if (FASE == 1 || (FASE == 2 && cc < nch)) mgp = max(mgp, gp < 0 ? -gp : gp);
-                if (FASE == 1) continue;
-                const int p = (int)((pw[k >> 2] >> (8 * (k & 3))) & 0xff);
-                if (FASE == 2) {
-                    if (cc < nch) s_part[k] += p * gp;
-                    else {
-                        const int ds = p * (gp - sl_s[16 * g + k]);
-                        mds = max(mds, ds < 0 ? -ds : ds);
-                        mp = max(mp, p);
+                for (int k = 0; k < 16; k++) {
+                    const bool dentro = k >= kmin;
+                    const int x = junta3(hh[k], cr[k], ll[k]);
+                    int gp;
+                    if (FASE == 1) gp = x;
+                    else if (RAP) gp = (x + meio1 + ((x >> sh) & 1)) >> sh;
+                    else gp = rnd_d(x, sh);
+                    gp = dentro ? gp : 0;
+                    if (FASE == 1 || (FASE == 2 && cc < nch)) mgp = max(mgp, gp < 0 ? -gp : gp);
+                    if (FASE == 1) continue;
+                    const int p = (int)((pw[k >> 2] >> (8 * (k & 3))) & 0xff);
+                    if (FASE == 2) {
+                        if (cc < nch) s_part[k] += p * gp;
+                        else {
+                            const int ds = p * (gp - sl_s[16 * g + k]);
+                            mds = max(mds, ds < 0 ? -ds : ds);
+                            mp = max(mp, p);
+                        }
+                    } else {
+                        const int y = p * (gp - sl_s[16 * g + k]);
+                        int ds;
+                        if (RAP) ds = (y + meio2 + ((y >> sh2) & 1)) >> sh2;
+                        else ds = rnd_d(y, sh2);
+                        ds = dentro ? ds : 0;
+                        digitos(ds, dh[k], dl[k]);
+                        ds_b[(2 * st) * TILE_NI + sw128(16 * g + k, jl)] = (uint8_t)dh[k];              // rows 0..63 of the stage's stacked tile
+                        ds_b[(2 * st + 1) * TILE_NI + sw128(16 * g + k, jl)] = (uint8_t)dl[k];          // rows 64..127
                     }
-                } else {
-                    const int ds = dentro ? rnd_d(p * (gp - sl_s[16 * g + k]), sh2) : 0;
-                    digitos(ds, dh[k], dl[k]);
-                    ds_b[(2 * st) * TILE_NI + sw128(16 * g + k, jl)] = (uint8_t)dh[k];              // rows 0..63 of the stage's stacked tile
-                    ds_b[(2 * st + 1) * TILE_NI + sw128(16 * g + k, jl)] = (uint8_t)dl[k];          // rows 64..127
                 }
-            }
+            };
+            const bool rapido = FASE == 1 || (sh >= 1 && sh <= 30 && (FASE != 3 || (sh2 >= 1 && sh2 <= 30)));
+            if (rapido) corpo(std::true_type{});
+            else corpo(std::false_type{});
             if (FASE == 3 && j < nzero) {
                 const size_t o = ((size_t)bh * T + j) * T + i0 + 16 * g;
                 grava16(A.DSh + o, dh);
