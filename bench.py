@@ -474,6 +474,21 @@ def mede_sweep(oc, reg, dev, reps=3):
 
 
 # ------------------------------------------------------------------------------------------------ training step
+def nucleos_por_passo(reg, c):
+    """Kernels of this library launched per step: one per recorded operation, except the attention on the tensor-core
+    path (head dimension 64, T >= 128), whose forward is 2 launches (operand preparation + the kernel) and whose backward is
+    5 (preparation, three row phases, the key-tile kernel).  The split-K memsets are not counted."""
+    from jatai_b200 import ops
+    n = len(reg.lancamentos)
+    if ops.BLK == 32 and c["D"] == 64 * c["H"] and c["T"] % 64 == 0 and 128 <= c["T"] <= 1024:
+        for lanc in reg.lancamentos:
+            if lanc["op"].startswith("atencao_back"):
+                n += 4
+            elif lanc["op"].startswith("atencao"):
+                n += 1
+    return n
+
+
 def resumo_perfil(reg):
     """Per-operation GPU time of one eager step (CUDA events around every launch), operation count and algorithmic bytes of its GEMMs."""
     tempos, ops_gemm, ms_gemm, alg = {}, 0.0, 0.0, 0.0
@@ -564,7 +579,7 @@ def mede_passo(c, rank, mundo, dev, steps, warmup, via=None, eager=False, biblio
     reg.novo_passo(1)
     m.passo(*lotes[1], k_lr=c["k_lr"])
     reg.fim_passo()
-    r["lancamentos"] = len(reg.lancamentos)
+    r["lancamentos"] = nucleos_por_passo(reg, c)
     if perfil:
         r["perfil"] = resumo_perfil(reg)
     reg.perfil = False
