@@ -19,6 +19,7 @@ optimiser.  Integer addition is associative, so the result is bit-identical to o
 """
 import math
 
+import os
 import torch
 
 from . import ops as O
@@ -345,7 +346,7 @@ class PassoGravado:
     the transposed copies made at the start of the step), so O_g may update it while the backward goes on.
     """
 
-    GRUPOS = 4          # data parallel: pieces of consecutive layers
+    GRUPOS = int(os.environ.get("JT_GRUPOS", "12"))         # data parallel: pieces of consecutive layers (measured: 12 beats 4 and 6)
 
     def __init__(self, modelo, Bt, T, k_lr):
         self.m, self.reg, self.k_lr = modelo, modelo.reg, k_lr
