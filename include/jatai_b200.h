@@ -45,6 +45,13 @@ void jt_gemm_split(int alvo_ctas);                         /* jatai_cuda.cu:1089
 void jt_gemm_bm(int bm);                                   /* jatai_cuda.cu:1090: accepted, ignored (tile height is fixed) */
 void jt_atencao_linhas(int n);                             /* jatai_cuda.cu:1091: accepted, ignored */
 int jt_res_estocastico(int ligado);                        /* jatai_cuda.cu:1087: only 0 is supported (bit parity) */
+/* No counterpart in the reference (its kernels never wait on one another).  Every wait of the tensor-core kernels on an
+ * mbarrier is bounded; jt_espera_limite sets the bound in SM clock cycles (<= 0: the default, about 2 s).  jt_teste_espera
+ * runs the bounded wait on its own - one warp, a barrier that nothing completes, no copy or MMA in flight - so that the
+ * give-up path can be exercised with a short limit: *saiu (a device int) becomes 2 and the error record holds code 7,
+ * place 99; the context stays usable. */
+int jt_espera_limite(long long ciclos);
+int jt_teste_espera(int* saiu, int kid);
 
 /* ---- GEMM: C[M,N] = A[M,K] . B[N,K]^T, operands blocked along K ---------------------------------- */
 /* modo 0 block output (Cm, CE) | 1 raw output (C32, Ce) | 2 block + residual add of X | 3 block h and

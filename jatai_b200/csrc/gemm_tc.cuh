@@ -54,6 +54,7 @@ struct Cfg {
     static constexpr uint32_t IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TNv >> 3) << 17) | ((uint32_t)(TM >> 4) << 24);
 };
 constexpr long long LIMITE_CICLOS = 4000000000LL;              // ~2 s at B200 clocks
+__device__ long long g_limite_espera = LIMITE_CICLOS;          // the limit in force (jt_espera_limite); read on the slow path of a wait only
 constexpr uint32_t MAGIA = 0x4B400000u;                        // bit pattern of 1.5 * 2^23
 constexpr float MAGIA_F = 12582912.0f;
 constexpr int DESLOC = 32 * 127 * 127;                         // the largest |partial product| of 32 int8 pairs
@@ -87,13 +88,27 @@ __device__ __forceinline__ bool espera(uint32_t bar, uint32_t par, volatile int*
             else if (*reinterpret_cast<volatile int*>(&g_erro.codigo) == E_TEMPO && *reinterpret_cast<volatile int*>(&g_erro.n) != 0) {
                 *aborta = 1;                     // a wait has already expired somewhere in this step: do not wait out another limit
                 return false;
-            } else if (agora - t0 > LIMITE_CICLOS) {
+            } else if (agora - t0 > *reinterpret_cast<volatile long long*>(&g_limite_espera)) {
                 *aborta = 1;
                 reporta(E_TEMPO, kid, onde, par, blockIdx.x + 65536LL * blockIdx.y);
                 return false;
             }
         }
     }
+}
+// The bounded wait on its own: one warp waits for a phase of an mbarrier that nothing ever completes, gives up when the limit
+// in force has passed, records E_TEMPO (place 99) and leaves normally.  No copy, MMA or other CTA is involved.
+__global__ void k_teste_espera(int kid, int* saiu) {
+    __shared__ __align__(8) unsigned long long barra;
+    __shared__ int aborta_s;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&barra), 1);
+        aborta_s = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    const bool ok = espera(smem_u32(&barra), 0, &aborta_s, kid, 99);
+    if (threadIdx.x == 0) *saiu = ok ? 1 : 2;                     // 2 = gave up, as it must
 }
 __device__ __forceinline__ void tma_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"

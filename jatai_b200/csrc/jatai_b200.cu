@@ -128,6 +128,17 @@ int jt_erro_le(long long* out) {
     out[0] = e.n; out[1] = e.codigo; out[2] = e.kid; out[3] = e.idx; out[4] = e.valor; out[5] = e.aux;
     return e.n;
 }
+// Limit of every bounded wait of the tensor-core kernels, in SM clock cycles (<= 0: back to the default of about 2 s).
+int jt_espera_limite(long long ciclos) {
+    const long long v = ciclos > 0 ? ciclos : tc::LIMITE_CICLOS;
+    return (int)cudaMemcpyToSymbol(tc::g_limite_espera, &v, sizeof(v));
+}
+// Self-test of the bounded wait: one warp waits on a barrier nothing completes and must give up after the limit in force
+// (set a short one first).  *saiu (device int) becomes 2 when it gave up; the error record then holds code 7, place 99.
+int jt_teste_espera(int* saiu, int kid) {
+    tc::k_teste_espera<<<1, 32, 0, g_stream>>>(kid, saiu);
+    return fim();
+}
 int jt_erro_limpa() {
     Erro e;
     memset(&e, 0, sizeof(e));

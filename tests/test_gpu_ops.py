@@ -473,3 +473,40 @@ def test_atencao_com_quant_fundido(amb, Bt, T, H, D, limite):
     assert reg.lancamentos[-1]["op"] == "atencao_back_quant"          # the fused entry point ran, not the composition
     compara(f"atencao_quant {Bt}/{T}/{H}/{D}", [*o_c, P_c], [*o_r, P_r])
     compara(f"atencao_back_quant {Bt}/{T}/{H}/{D} limite={limite}", list(g_c), list(g_r))
+
+
+@pytest.mark.gpu
+def test_espera_limitada_desiste_e_o_contexto_segue(amb):
+    """The bounded wait of the tensor-core kernels on its own: one warp waits on a barrier that nothing completes, gives up
+    after the (shortened) limit, records code 7 at place 99 and returns; the next GEMM is bit-exact as ever.  No copy,
+    MMA or second CTA is involved, and the wait is the library's own `espera`."""
+    import ctypes
+    import json
+    import time
+    ops, oc, reg = amb
+    lib = oc.lib
+    ops.define_blk(32)
+    torch.cuda.synchronize()
+    assert lib.jt_erro_limpa() == 0
+    saiu = torch.zeros(1, dtype=torch.int32, device=DEV)
+    assert lib.jt_espera_limite(ctypes.c_longlong(2_000_000)) == 0          # about a millisecond
+    try:
+        t0 = time.time()
+        assert lib.jt_teste_espera(ctypes.c_void_p(saiu.data_ptr()), ctypes.c_int(5)) == 0
+        torch.cuda.synchronize()
+        dt = time.time() - t0
+        out = (ctypes.c_longlong * 6)()
+        n = lib.jt_erro_le(out)
+        assert saiu.item() == 2, "the wait must give up"
+        assert n >= 1 and out[1] == 7 and out[2] == 5 and out[3] == 99, list(out)
+        assert dt < 2.0, f"gave up after {dt:.2f} s with a limit of about 1 ms"
+    finally:
+        assert lib.jt_espera_limite(ctypes.c_longlong(0)) == 0
+        assert lib.jt_erro_limpa() == 0
+    reg.novo_passo(0)
+    with open(os.path.join(gu.AQUI, "config1_b32.json")) as fh:
+        rec = json.load(fh)
+    X, W, _ = (para_gpu(t) for t in casos.config1(32))
+    Y = oc.gemm(X, W)
+    torch.cuda.synchronize()
+    assert [gu.digest(t) for t in Y] == rec["Y"]
