@@ -53,7 +53,7 @@ CONFIGS = {
 SWEEP = [(16384, 4096, 4096), (16384, 4096, 16384), (16384, 16384, 4096)]        # benchmark configuration 2
 # DRAM bytes read + written per launch of the tensor-core GEMM, from one ncu capture (1 launch, --clock-control none,
 # cold L2) of the 4096 x 4096 x 4096 block GEMM; other shapes scale by their algorithmic bytes (traffic grows with them)
-TRAFEGO_NCU = dict(bytes=36.9e6, forma=(4096, 4096, 4096), fonte="ncu dram__bytes_read.sum + dram__bytes_write.sum, k_gemm_tc 4096x4096x4096, 1 launch")
+TRAFEGO_NCU = dict(bytes=35.2e6, forma=(4096, 4096, 4096), fonte="ncu dram__bytes_read.sum + dram__bytes_write.sum, k_gemm_tc 4096x4096x4096, 1 launch")
 
 
 # ------------------------------------------------------------------------------------------------ helpers
