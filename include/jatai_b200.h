@@ -140,6 +140,13 @@ int jt_rms_back_soma(const void* gm, const void* gE, const void* ym, const void*
  * a weight-gradient GEMM.  Same results as the two calls. */
 int jt_transpoe2(const void* X1, const void* EX1, void* Y1, void* EY1, const void* X2, const void* EX2, void* Y2, void* EY2, int C1, int C2,
                  int R, int kid);
+/* The same, and jt_max_linha of both results: RM1 [C1] and RM2 [C2] (int8, 4-byte aligned, PRE-SET TO -128 BY THE CALLER)
+ * receive the largest block exponent of every row of Y1 / Y2 (maximum into what is there).  Data parallel uses it to have
+ * the row maxima of its weight-gradient operands written straight into the buffer of the MAX collective.  Block 32 and
+ * C1, C2 multiples of 256 only (cudaErrorNotSupported otherwise: call jt_transpoe2 and jt_max_linha).  No counterpart in
+ * the reference. */
+int jt_transpoe2_max(const void* X1, const void* EX1, void* Y1, void* EY1, const void* X2, const void* EX2, void* Y2, void* EY2, void* RM1,
+                     void* RM2, int C1, int C2, int R, int kid);
 
 /* jt_atencao_back for callers that may not allocate device memory (fixed memory budgets, code running where
  * cudaMalloc is forbidden): same arguments and results, but the workspace lives in a fixed 4 MiB device array

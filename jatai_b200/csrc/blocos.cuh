@@ -380,7 +380,7 @@ __global__ void __launch_bounds__(256) k_transpoe(const int8_t* __restrict__ X, 
 // (|m| <= 127 going in).  Blocks whose exponents are more than 100 apart take an integer path.
 constexpr int T32_PW = 256 / 4 + 1;
 // integer path of k_transpoe32 for one column of a block whose exponents are too far apart for fp32 (cold)
-__device__ __noinline__ void transpoe32_lento(const uint32_t (*tile)[T32_PW], const int8_t (*et)[8], int rb, int cw, int k, int8_t* dst,
+__device__ __noinline__ int transpoe32_lento(const uint32_t (*tile)[T32_PW], const int8_t (*et)[8], int rb, int cw, int k, int8_t* dst,
                                               int8_t* Edst, int kid, long long idx0) {
     int v[32], e[32], q[32];
 #pragma unroll
@@ -392,11 +392,25 @@ __device__ __noinline__ void transpoe32_lento(const uint32_t (*tile)[T32_PW], co
 #pragma unroll
     for (int i4 = 0; i4 < 8; i4++) reinterpret_cast<uint32_t*>(dst)[i4] = junta4(q[4 * i4], q[4 * i4 + 1], q[4 * i4 + 2], q[4 * i4 + 3]);
     *Edst = (int8_t)Eo;
+    return Eo;
+}
+
+// per-byte signed maximum into a 4-byte-aligned word of an int8 array
+__device__ __forceinline__ void max4_atomico(int8_t* p, uint32_t meu) {
+    unsigned* w = reinterpret_cast<unsigned*>(p);
+    unsigned visto = *w;
+    for (;;) {
+        const unsigned novo = __vmaxs4(visto, meu);
+        if (novo == visto) return;
+        const unsigned antes = atomicCAS(w, visto, novo);
+        if (antes == visto) return;
+        visto = antes;
+    }
 }
 
 template <int TR, int CPT>
 __device__ __forceinline__ void transpoe32_corpo(const int8_t* __restrict__ X, const int8_t* __restrict__ EX, int8_t* __restrict__ Y,
-                                                 int8_t* __restrict__ EY, int R, int C, int kid) {
+                                                 int8_t* __restrict__ EY, int R, int C, int kid, int8_t* __restrict__ RM = nullptr) {
     static_assert(CPT == 4 || CPT == 1, "a thread owns the 4 columns of a word or one of them");
     constexpr int TC = 256, PW = T32_PW, NT = 8 * TR / CPT, NPAR = (TR / 32) * 8;
     __shared__ uint32_t tile[TR][PW];
@@ -434,6 +448,7 @@ __device__ __forceinline__ void transpoe32_corpo(const int8_t* __restrict__ X, c
     const int eref = (int)(int16_t)(er & 0xffff);
     const bool largo = (er >> 30) & 1;                              // spread too wide for the fp32 path
     const float* fa = &fA[rb * 32][cw >> 3];
+    uint32_t emax4 = 0x80808080u;                                   // the new exponents of this thread's columns, -128 where it has none
 #pragma unroll
     for (int k = 0; k < 4; k++) {
         if (CPT == 1 && k != k_meu) continue;
@@ -441,7 +456,8 @@ __device__ __forceinline__ void transpoe32_corpo(const int8_t* __restrict__ X, c
         int8_t* dst = Y + col * R + r0 + rb * 32;
         int8_t* Edst = EY + col * nby + (r0 + rb * 32) / 32;
         if (largo) {
-            transpoe32_lento(tile, et, rb, cw, k, dst, Edst, kid, (long long)col * R + r0 + rb * 32);
+            const int Eo = transpoe32_lento(tile, et, rb, cw, k, dst, Edst, kid, (long long)col * R + r0 + rb * 32);
+            emax4 = (emax4 & ~(0xffu << (8 * k))) | ((uint32_t)(uint8_t)(int8_t)Eo << (8 * k));
             continue;
         }
         float t[32], mx = 0.f;
@@ -467,7 +483,10 @@ __device__ __forceinline__ void transpoe32_corpo(const int8_t* __restrict__ X, c
         reinterpret_cast<uint4*>(dst)[0] = make_uint4(saida[0], saida[1], saida[2], saida[3]);
         reinterpret_cast<uint4*>(dst)[1] = make_uint4(saida[4], saida[5], saida[6], saida[7]);
         *Edst = (int8_t)Eo;
+        emax4 = (emax4 & ~(0xffu << (8 * k))) | ((uint32_t)(uint8_t)(int8_t)Eo << (8 * k));
     }
+    // row maxima of the transposed tensor (what a GEMM aligns its rows to): the caller pre-set RM to -128
+    if (RM != nullptr) max4_atomico(RM + c0 + 4 * cw, emax4);
 }
 
 template <int TR, int CPT = 4>
@@ -479,12 +498,12 @@ __global__ void __launch_bounds__(8 * TR / CPT, 768 / (8 * TR / CPT)) k_transpoe
 
 // Two transpositions of matrices with the same number of rows in one launch (the two operands of a weight-gradient
 // GEMM): blockIdx.z picks the matrix, the grid is as wide as the wider one.
-struct ArgsTransp { const int8_t* X; const int8_t* EX; int8_t* Y; int8_t* EY; int C; };
+struct ArgsTransp { const int8_t* X; const int8_t* EX; int8_t* Y; int8_t* EY; int C; int8_t* RM; };
 template <int TR, int CPT = 4>
 __global__ void __launch_bounds__(8 * TR / CPT, 768 / (8 * TR / CPT)) k_transpoe32_par(ArgsTransp a0, ArgsTransp a1, int R, int kid) {
     const ArgsTransp a = blockIdx.z ? a1 : a0;
     if ((int)blockIdx.x * 256 >= a.C) return;
-    transpoe32_corpo<TR, CPT>(a.X, a.EX, a.Y, a.EY, R, a.C, kid);
+    transpoe32_corpo<TR, CPT>(a.X, a.EX, a.Y, a.EY, R, a.C, kid, a.RM);
 }
 
 // RMSNorm without gain, one warp per row, NP*512 >= D columns held in registers.  ops.py:153-165

@@ -264,12 +264,16 @@ int jt_transpoe(const void* X, const void* EX, void* Y, void* EY, int R, int C, 
     else k_transpoe<128><<<grade, 256, 0, g_stream>>>((const int8_t*)X, (const int8_t*)EX, (int8_t*)Y, (int8_t*)EY, R, C, kid);
     return fim();
 }
-int jt_transpoe2(const void* X1, const void* EX1, void* Y1, void* EY1, const void* X2, const void* EX2, void* Y2, void* EY2, int C1, int C2,
-                 int R, int kid) {
+// the pair of transpositions; RM1 / RM2 (optional, both or none): int8 [C1] / [C2], pre-set to -128 by the caller, receive the
+// row maxima of the exponents of Y1 / Y2 (what jt_max_linha would compute from EY1 / EY2)
+static int transpoe2_impl(const void* X1, const void* EX1, void* Y1, void* EY1, const void* X2, const void* EX2, void* Y2, void* EY2, int C1, int C2,
+                          int R, void* RM1, void* RM2, int kid) {
     if (R <= 0 || C1 <= 0 || C2 <= 0 || R % 128) return (int)cudaErrorInvalidValue;
+    const bool com_max = RM1 != nullptr || RM2 != nullptr;
+    if (com_max && (RM1 == nullptr || RM2 == nullptr || (((uintptr_t)RM1 | (uintptr_t)RM2) & 3) != 0)) return (int)cudaErrorInvalidValue;
     if (g_blk == 32 && C1 % 256 == 0 && C2 % 256 == 0 && (((uintptr_t)EX1 | (uintptr_t)EX2) & 3) == 0) {
-        const ArgsTransp a0 = {(const int8_t*)X1, (const int8_t*)EX1, (int8_t*)Y1, (int8_t*)EY1, C1};
-        const ArgsTransp a1 = {(const int8_t*)X2, (const int8_t*)EX2, (int8_t*)Y2, (int8_t*)EY2, C2};
+        const ArgsTransp a0 = {(const int8_t*)X1, (const int8_t*)EX1, (int8_t*)Y1, (int8_t*)EY1, C1, (int8_t*)RM1};
+        const ArgsTransp a1 = {(const int8_t*)X2, (const int8_t*)EX2, (int8_t*)Y2, (int8_t*)EY2, C2, (int8_t*)RM2};
         const int cx = (C1 > C2 ? C1 : C2) / 256;
         const long long t128 = (long long)((C1 + C2) / 256) * (R / 128);
         if (t128 >= 148) k_transpoe32_par<128><<<dim3(cx, R / 128, 2), 256, 0, g_stream>>>(a0, a1, R, kid);
@@ -278,8 +282,18 @@ int jt_transpoe2(const void* X1, const void* EX1, void* Y1, void* EY1, const voi
         else k_transpoe32_par<32, 1><<<dim3(cx, R / 32, 2), 256, 0, g_stream>>>(a0, a1, R, kid);
         return fim();
     }
+    if (com_max) return (int)cudaErrorNotSupported;            // the maxima are written by the wide block-32 kernel only
     const int c = jt_transpoe(X1, EX1, Y1, EY1, R, C1, kid);
     return c ? c : jt_transpoe(X2, EX2, Y2, EY2, R, C2, kid);
+}
+int jt_transpoe2(const void* X1, const void* EX1, void* Y1, void* EY1, const void* X2, const void* EX2, void* Y2, void* EY2, int C1, int C2,
+                 int R, int kid) {
+    return transpoe2_impl(X1, EX1, Y1, EY1, X2, EX2, Y2, EY2, C1, C2, R, nullptr, nullptr, kid);
+}
+int jt_transpoe2_max(const void* X1, const void* EX1, void* Y1, void* EY1, const void* X2, const void* EX2, void* Y2, void* EY2, void* RM1,
+                     void* RM2, int C1, int C2, int R, int kid) {
+    if (RM1 == nullptr || RM2 == nullptr) return (int)cudaErrorInvalidValue;
+    return transpoe2_impl(X1, EX1, Y1, EY1, X2, EX2, Y2, EY2, C1, C2, R, RM1, RM2, kid);
 }
 int jt_embed(const void* Wm, const void* WE, const void* tok, void* Xm, void* XE, int M, int D, int V, int kid) {
     if (M <= 0 || D <= 0 || D % g_blk) return (int)cudaErrorInvalidValue;

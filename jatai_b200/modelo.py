@@ -95,6 +95,24 @@ class Modelo:
             return par(gy, x)
         return self.ops.transpoe(gy), self.ops.transpoe(x)
 
+    def _transpoe_par_max(self, gy, x):
+        """Data parallel: both operands of a weight-gradient GEMM transposed, with their row maxima - written by the
+        transposition itself into the reducer's buffer where the launcher and the reducer offer that, by max_linha otherwise."""
+        ops, red = self.ops, self.redutor
+        junto, fatias = getattr(ops, "transpoe2_max", None), getattr(red, "fatias_max", None)
+        if junto is not None and fatias is not None and gy[0].shape[0] == x[0].shape[0] and gy[0].shape[1] % 256 == 0 and x[0].shape[1] % 256 == 0:
+            f = fatias(gy[0].shape[1], x[0].shape[1])
+            if f is not None:
+                par = junto(gy, x, f[0], f[1])
+                if par is not None:
+                    return par[0], par[1], f[0], f[1]
+                a, b = self._transpoe_par(gy, x)                    # the slices are taken: fill them the long way
+                f[0].copy_(ops.max_linha(a))
+                f[1].copy_(ops.max_linha(b))
+                return a, b, f[0], f[1]
+        a, b = self._transpoe_par(gy, x)
+        return a, b, ops.max_linha(a), ops.max_linha(b)
+
     def _grad_peso(self, nome, gy, x):
         """dW = gy^T . x as a raw tensor.  Both operands are transposed so that the reduced dimension (tokens)
         is the blocked one.  Data parallel: the GEMM is deferred - only the transposed operands and their row
@@ -119,12 +137,12 @@ class Modelo:
             ops.lib.jt_stream(self._lado.cuda_stream)
             try:
                 self._otimiza_pendente()
-                a, b = self._transpoe_par(gy, x)
                 if self.redutor is None:
+                    a, b = self._transpoe_par(gy, x)
                     self._grads[nome] = ops.gemm(a, b, cru=True)
                     self._pendente = nome
                 else:       # data parallel: only the transpositions and the row maxima now, the GEMM after the exchange
-                    self._adiados.append((nome, a, b, ops.max_linha(a), ops.max_linha(b)))
+                    self._adiados.append((nome, *self._transpoe_par_max(gy, x)))
             finally:
                 ops.lib.jt_stream(principal.cuda_stream)
 
@@ -247,6 +265,9 @@ class Modelo:
         self._grads, self._adiados = {}, []
         self._pendente, self._feitos = None, set()
         self._k_lr_lado = k_lr if (self.redutor is None and self._lado is not None) else None
+        inicio = getattr(self.redutor, "inicio_passo", None) if treina else None
+        if inicio is not None:
+            inicio()                                               # data parallel: the buffer of row maxima starts the step at -128
         guardados = []
         wt = self._pesos_transpostos() if treina else {}
         with reg.trecho("forward"):
@@ -392,9 +413,10 @@ class PassoGravado:
                 maximos = red.vistas_maximos([(ra, rb) for _, _, _, ra, rb in adiados])
                 nomes = [a[0] for a in adiados]
                 self._lado = torch.cuda.Stream(device=modelo.dev)
-                pool_l, vistas_g = None, []
-                with torch.cuda.stream(self._lado):
-                    for g, (a0, a1) in enumerate(grupos):
+                self._lado2 = torch.cuda.Stream(device=modelo.dev)
+                pool_l, pool_o, vistas_g = None, None, []
+                for g, (a0, a1) in enumerate(grupos):
+                    with torch.cuda.stream(self._lado):
                         gd = torch.cuda.CUDAGraph()
                         with torch.cuda.graph(gd, stream=self._lado, **({} if pool_l is None else {"pool": pool_l})):
                             lib.jt_stream(torch.cuda.current_stream().cuda_stream)
@@ -402,15 +424,19 @@ class PassoGravado:
                             modelo._gemms_adiados(maximos, a0, a1)
                             v, fatia = red.empacota_grupo({k: modelo._grads[k] for k in nomes[a0:a1]}, modelo._grads)
                         pool_l = gd.pool()
+                    # the optimiser graphs run on a third stream with a pool of their own: while piece g's sums are on the wire
+                    # and being applied, the second stream already runs the GEMMs of piece g + 1
+                    with torch.cuda.stream(self._lado2):
                         go = torch.cuda.CUDAGraph()
-                        with torch.cuda.graph(go, stream=self._lado, pool=pool_l):
+                        with torch.cuda.graph(go, stream=self._lado2, **({} if pool_o is None else {"pool": pool_o})):
                             lib.jt_stream(torch.cuda.current_stream().cuda_stream)
                             with self.reg.trecho("otimizador"):
                                 modelo._otimiza(v, k_lr)
-                        self._D.append(gd)
-                        self._O.append(go)
-                        self._fatias.append(fatia)
-                        vistas_g.append(v)
+                        pool_o = go.pool()
+                    self._D.append(gd)
+                    self._O.append(go)
+                    self._fatias.append(fatia)
+                    vistas_g.append(v)
                 self._vivos = (adiados, vistas_g, dict(modelo._grads), maximos)
                 self.grafos = self._M + self._D + self._O
         finally:
@@ -436,7 +462,9 @@ class PassoGravado:
                 pronto_max.wait()
                 gd.replay()
                 pronto = red.reduz_fatia(*fsoma)                  # asynchronous: ordered after this piece's GEMMs
-                pronto.wait()
-                go.replay()
-        principal.wait_stream(self._lado)                         # the next step reads every weight
+            with torch.cuda.stream(self._lado2):
+                pronto.wait()                                     # the second stream does not wait for the sums: it goes on
+                go.replay()                                       # with the next piece's GEMMs
+        principal.wait_stream(self._lado)
+        principal.wait_stream(self._lado2)                        # the next step reads every weight
         return self.perda

@@ -32,7 +32,7 @@ _INT_FUNCS = ("jt_gemm", "jt_gemm_f", "jt_gemm_ext", "jt_max_linha", "jt_quant",
               "jt_momento", "jt_peso", "jt_momento_peso", "jt_transpoe", "jt_transpoe2", "jt_embed", "jt_um_quente", "jt_rms", "jt_rms_back", "jt_rms_back_soma", "jt_atencao",
               "jt_atencao_back", "jt_softmax_ce", "jt_erro_le", "jt_erro_limpa", "jt_sincroniza", "jt_para16", "jt_para8",
               "jt_soma16", "jt_res_estocastico", "jt_blk", "jt_blk_atual", "jt_gemm_via", "jt_gemm_tn", "jt_atencao_back_fixo", "jt_atencao_via", "jt_atencao_quant", "jt_atencao_back_quant",
-              "jt_espera_limite", "jt_teste_espera")
+              "jt_espera_limite", "jt_teste_espera", "jt_transpoe2_max")
 
 
 def g_rms(D):
@@ -204,6 +204,24 @@ class OpsCuda:
         Y1, Y2 = self._bloco_vazio(C1, R, m1.device), self._bloco_vazio(C2, R, m1.device)
         self._lanca("transpoe2", "jt_transpoe2", (m1, E1, Y1[0], Y1[1], m2, E2, Y2[0], Y2[1]), (C1, C2, R), dict(X1=m1, EX1=E1, X2=m2, EX2=E2),
                     (C1 + C2, R))
+        return Y1, Y2
+
+    def transpoe2_max(self, X1, X2, R1, R2):
+        """transpoe2, and the row maxima of both results (max_linha) written into R1 [C1] / R2 [C2] - int8 views the caller has
+        pre-set to -128 (data parallel: slices of the buffer of its MAX collective).  None where this library or these
+        shapes do not offer it (the caller then uses transpoe2 and max_linha)."""
+        (m1, E1), (m2, E2) = X1, X2
+        R, C1 = m1.shape
+        C2 = m2.shape[1]
+        if BLK != 32 or C1 % 256 or C2 % 256 or R % 128 or m2.shape[0] != R or not hasattr(self.lib, "jt_transpoe2_max"):
+            return None
+        self.reg.confere_bloco("X1", X1)
+        self.reg.confere_bloco("X2", X2)
+        self.reg.exige(R1.numel() == C1 and R2.numel() == C2 and R1.dtype == torch.int8 and R2.dtype == torch.int8 and
+                       R1.data_ptr() % 4 == 0 and R2.data_ptr() % 4 == 0, "transpoe2_max: row-maximum views of the wrong size, type or alignment")
+        Y1, Y2 = self._bloco_vazio(C1, R, m1.device), self._bloco_vazio(C2, R, m1.device)
+        self._lanca("transpoe2", "jt_transpoe2_max", (m1, E1, Y1[0], Y1[1], m2, E2, Y2[0], Y2[1], R1, R2), (C1, C2, R),
+                    dict(X1=m1, EX1=E1, X2=m2, EX2=E2), (C1 + C2, R))
         return Y1, Y2
 
     # ------------------------------------------------------------------ block elementwise

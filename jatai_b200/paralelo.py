@@ -52,11 +52,33 @@ class Redutor:
         self.reduz_maximos()
         return self.vistas_maximos(pares)
 
+    def inicio_passo(self):
+        """Start of a training step: once the flat buffer of row maxima exists (from the second step on) it is pre-set to -128
+        so that the transposition kernels can write their maxima straight into it (`fatias_max`)."""
+        self._cursor_max = 0
+        if getattr(self, "_max", None) is not None:
+            self._max.fill_(-128)
+
+    def fatias_max(self, na, nb):
+        """The next two slices (na and nb int8 entries) of the flat buffer, in the order the step produces its weight-gradient
+        operands - the same order `empacota_maximos` uses - or None while the buffer does not exist yet (first step) or the
+        request does not fit (the caller then computes the maxima apart and they are copied in)."""
+        m = getattr(self, "_max", None)
+        o = getattr(self, "_cursor_max", None)
+        if m is None or o is None or o + na + nb > m.numel() or o % 4 or na % 4:
+            self._cursor_max = None                                  # out of step with the plan: no more in-place slices this step
+            return None
+        self._cursor_max = o + na + nb
+        return m[o:o + na], m[o + na:o + na + nb]
+
     def empacota_maximos(self, pares, o=0):
-        """Copies local maxima into the flat buffer from offset `o` on; returns the offset after them."""
+        """Puts local maxima into the flat buffer from offset `o` on (those written in place by `fatias_max` are there
+        already); returns the offset after them."""
+        base = self._max.data_ptr()
         for ra, rb in pares:
             for r in (ra, rb):
-                self._max[o:o + r.numel()].copy_(r)
+                if r.data_ptr() != base + o:
+                    self._max[o:o + r.numel()].copy_(r)
                 o += r.numel()
         return o
 

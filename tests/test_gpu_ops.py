@@ -510,3 +510,26 @@ def test_espera_limitada_desiste_e_o_contexto_segue(amb):
     Y = oc.gemm(X, W)
     torch.cuda.synchronize()
     assert [gu.digest(t) for t in Y] == rec["Y"]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("R,C1,C2,esp", [(256, 256, 512, 8), (2048, 512, 1536, 3), (128, 256, 256, 40), (4096, 2048, 512, 60), (8192, 2048, 2048, 5)])
+def test_transpoe_par_com_maximos(amb, R, C1, C2, esp):
+    """jt_transpoe2_max = jt_transpoe2 followed by jt_max_linha of both results, bit for bit, with the maxima written (as a
+    maximum into a buffer pre-set to -128) by the transposition kernel itself: every tile height, exponents far apart (the
+    integer path of the kernel), all-zero blocks."""
+    ops, oc, reg = amb
+    ops.define_blk(32)
+    reg.novo_passo(0)
+    G = casos.Gen(900 + R + C1 + C2, 32)
+    d1, d2 = para_gpu(G.bloco(R, C1, espalha=esp, zera=0.1)), para_gpu(G.bloco(R, C2, espalha=3, zera=0.3))
+    separados = oc.transpoe2(d1, d2)
+    r1, r2 = oc.max_linha(separados[0]), oc.max_linha(separados[1])
+    buf = torch.full((C1 + C2 + 256,), -128, dtype=torch.int8, device=DEV)
+    juntos = oc.transpoe2_max(d1, d2, buf[256:256 + C1], buf[256 + C1:])
+    torch.cuda.synchronize()
+    assert juntos is not None
+    compara(f"transpoe2_max {R}x({C1},{C2})", casos.plano(juntos), casos.plano(separados))
+    assert torch.equal(buf[256:256 + C1], r1) and torch.equal(buf[256 + C1:], r2)
+    assert bool((buf[:256] == -128).all())
+    assert oc.transpoe2_max(para_gpu(G.bloco(128, 192, espalha=2, zera=0.0)), para_gpu(G.bloco(128, 256, espalha=2, zera=0.0)), buf[:192], buf[256:512]) is None
