@@ -355,12 +355,12 @@ class PassoGravado:
 
     Data parallel: no collective is ever part of a captured graph; the step is cut into GRUPOS pieces of consecutive layers
     and recorded as 3 graphs per piece, with the collectives issued eagerly between the replays:
-        M_g  forward (g = 0) and the backward of piece g, the transpositions and row maxima of its weight-gradient operands
-             on the side branch, the maxima packed into their slice of the flat buffer                      main stream
+        M_g  forward (g = 0) and the backward of piece g, the transpositions of its weight-gradient operands on the side
+             branch, writing their row maxima into the piece's slice of the flat buffer                     main stream
         MAX  all-reduce of that slice (a few KB, on a communicator of its own)
         D_g  the weight-gradient GEMMs of piece g with the global maxima, sums packed into the flat buffer   second stream
         SUM  all-reduce of the piece's int32 sums (asynchronous)
-        O_g  the optimiser step of the piece's weights                                                      second stream
+        O_g  the optimiser step of the piece's weights                                                      third stream
     The main stream goes straight on to M_{g+1} after queueing MAX_g, so the weight-gradient GEMMs, the gradient traffic and
     the optimiser of piece g run beside the backward of piece g + 1, as the single-GPU step runs them beside its backward;
     only the last piece's tail is exposed.  The backward never reads a weight again after its own piece (it multiplies by
