@@ -729,11 +729,11 @@ def braco_passo(args):
 
 
 # ------------------------------------------------------------------------------------------------ fused op suite
-def mede_ops(dev, reps=12, warmup=3):
+def mede_ops(dev, reps=12, warmup=3, tokens=16384):
     """Benchmark configuration 3: the bandwidth-bound ops at 16384 tokens x D=1024 (block 32); achieved HBM GB/s per op from
     the algorithmic bytes (inputs read once + outputs written once).  Inputs rotate over enough copies to exceed L2."""
     ops, oc, reg = lanca_ops(BLK, "ops")
-    M, D, FF, V, NW = 16384, 1024, 4096, 256, 12 * 1024 * 1024
+    M, D, FF, V, NW = tokens, 1024, 4096, 256, 12 * 1024 * 1024
     g = torch.Generator().manual_seed(7)
 
     def bloco(R, C, e0=-10, esp=4):
@@ -757,7 +757,8 @@ def mede_ops(dev, reps=12, warmup=3):
     ys = [oc.rms(t) for t in x]
     gs = copias(lambda: bloco(M, D, e0=-20), 6)
     casos_.append(("rms_back", M * (3 * D * b1 + 8), [lambda a=a, y=y: oc.rms_back(a, y[0], y[1]) for a, y in zip(gs, ys)]))
-    casos_.append(("soma", 3 * M * D * b1, [lambda a=a, b=b: oc.soma(a, b) for a, b in zip(x, gs)]))
+    x2 = copias(lambda: bloco(M, D), 6)          # both operands of the add from the stated distribution (block exponents uniform over 9 values)
+    casos_.append(("soma", 3 * M * D * b1, [lambda a=a, b=b: oc.soma(a, b) for a, b in zip(x, x2)]))
     h = copias(lambda: bloco(M, FF), 3)
     h2 = copias(lambda: bloco(M, FF), 3)
     casos_.append(("relu2", 2 * M * FF * b1, [lambda t=t: oc.relu2(t) for t in h]))
@@ -776,6 +777,7 @@ def mede_ops(dev, reps=12, warmup=3):
     casos_.append(("peso", NW * 5 * b1, [lambda a=a, b=b, r=r: oc.peso(a, b, r, 4, True) for a, b, r in zip(w, mom, res)]))
     casos_.append(("momento_peso (one launch)", NW * (6 + 7 * b1), [lambda a=a, b=b, ww=ww, r=r: oc.momento_peso(a, b, ww, r, 4, True) for a, b, ww, r in zip(gw, mom, w, res)]))
     Bt, T, H = 16, 1024, 16
+    M_ops, M = M, Bt * T                       # the attention keeps its shape whatever the row count of the other ops
     qkv = copias(lambda: bloco(M, 3 * D, esp=3), 2)
     b_at = M * 3 * D * b1 + M * D * 6 + Bt * H * T * T
     casos_.append(("atencao (16 seq x 16 heads x T=1024, hd 64)", b_at, [lambda t=t: oc.atencao(t, Bt, T, H) for t in qkv]))
@@ -822,14 +824,14 @@ def mede_ops(dev, reps=12, warmup=3):
     agg = tot_b / (tot_ms * 1e-3) / 1e9
     return {"per_op": tabela, "aggregate_GBs": agg, "aggregate_frac_of_measured_hbm": agg / pk["hbm_gbs"], "hbm_peak_GBs": pk["hbm_gbs"],
             "peak_source": f"STREAM-style copy ({pk['origem']})", "reps": reps, "ms_total": tot_ms, "launches": n_lanc,
-            "workload": "ops_16384tok_D1024_b32", "l2": "inputs rotate over copies totalling more than L2 (126 MB)",
+            "workload": f"ops_{M_ops}tok_D1024_b32", "l2": "inputs rotate over copies totalling more than L2 (126 MB)",
             "timing": "each op recorded `reps` times in a CUDA graph over rotating inputs; the replay is timed with CUDA events",
             "aggregate_note": "bandwidth ops only; the two attention lines are contractions and are listed for their time"}
 
 
 def braco_ops(args):
     rank, mundo, dev = inicia_gpu()
-    r = mede_ops(dev, reps=max(args.steps, 5), warmup=max(args.warmup, 3))
+    r = mede_ops(dev, reps=max(args.steps, 5), warmup=max(args.warmup, 3), tokens=args.tokens)
     if rank != 0:
         return
     print(json.dumps({
@@ -853,6 +855,7 @@ def main():
     ap.add_argument("--via", type=int, default=None, help="force a GEMM path (jt_gemm_via)")
     ap.add_argument("--eager", action="store_true", help="passo: no CUDA graph")
     ap.add_argument("--forma", type=int, nargs=3, default=None, metavar=("M", "K", "N"), help="gemm: another shape (profiling captures)")
+    ap.add_argument("--tokens", type=int, default=16384, help="ops: rows of the op suite (configuration 3 is 16384; larger sizes show the kernels without the launch overhead)")
     ap.add_argument("--sem-cpu", dest="sem_cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--sem-extras", dest="sem_extras", action="store_true", help="passo: headline only, no extra legs")
     ap.add_argument("--biblioteca", default=None, help="passo: another library with the same C ABI (diagnostics; block length of --config must suit it)")

@@ -122,11 +122,29 @@ __global__ void __launch_bounds__(256) k_soma(const int8_t* __restrict__ xm, con
 #pragma unroll
     for (int k = 0; k < U; k++) {
         JT_PEDACO(k)
-        int xv[16], yv[16];
-        desempacota16(rx[k], xv);
-        desempacota16(ry[k], yv);
         uint4 pac;
-        const int Eo = soma16<GL>(xv, ex[k], yv, ey[k], pac, kid, o);
+        int Eo;
+        // fp32 path: with the exponents at most 16 apart w = hi * 2^d + lo is below 2^24, exact in fp32, and the fp32 quantiser
+        // gives the bits of the integer one; an all-zero block on either side leaves the other operand alone.  Taken by a
+        // whole warp or not at all (the quantisers shuffle inside the lane groups of a block).
+        const bool x_maior = ex[k] >= ey[k];
+        const int eH = x_maior ? ex[k] : ey[k], eL = x_maior ? ey[k] : ex[k];
+        const uint4 rl = x_maior ? ry[k] : rx[k];
+        const int d = (eL == E_ZERO && (rl.x | rl.y | rl.z | rl.w) == 0) ? 0 : eH - eL;
+        if (__all_sync(FULL, d <= 16)) {
+            float fx[16], fy[16];
+            bytes_para_float(rx[k], fx);
+            bytes_para_float(ry[k], fy);
+            const float a = x_maior ? __int_as_float((127 + d) << 23) : 1.f, b = x_maior ? 1.f : __int_as_float((127 + d) << 23);
+#pragma unroll
+            for (int i = 0; i < 16; i++) fx[i] = fmaf(fx[i], a, fy[i] * b);
+            Eo = quant_f32<GL>(fx, eH - d, pac, kid, o);
+        } else {
+            int xv[16], yv[16];
+            desempacota16(rx[k], xv);
+            desempacota16(ry[k], yv);
+            Eo = soma16<GL>(xv, ex[k], yv, ey[k], pac, kid, o);
+        }
         if (ativo) *reinterpret_cast<uint4*>(zm + o) = pac;
         if (lider) zE[w] = (int8_t)Eo;
     }

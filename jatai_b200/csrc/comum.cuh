@@ -219,14 +219,16 @@ __device__ __forceinline__ int quant_geral(const int (&v)[NV], const int (&e)[NV
     return E;
 }
 
+// 16 int8 -> float without the conversion pipe: with its sign bit flipped a byte is b + 128 in 0..255; placed under the upper
+// bytes of 1.5 * 2^23 it reads as the float 12582912 + 128 + b, and one subtraction leaves b exactly.
 __device__ __forceinline__ void bytes_para_float(const uint4& r, float (&f)[16]) {
-    const uint32_t u[4] = {r.x, r.y, r.z, r.w};
+    const uint32_t u[4] = {r.x ^ 0x80808080u, r.y ^ 0x80808080u, r.z ^ 0x80808080u, r.w ^ 0x80808080u};
 #pragma unroll
     for (int i = 0; i < 4; i++) {
-        f[4 * i + 0] = (float)(int)(int8_t)(u[i] & 0xff);
-        f[4 * i + 1] = (float)(int)(int8_t)((u[i] >> 8) & 0xff);
-        f[4 * i + 2] = (float)(int)(int8_t)((u[i] >> 16) & 0xff);
-        f[4 * i + 3] = (float)((int)u[i] >> 24);
+        f[4 * i + 0] = __uint_as_float(__byte_perm(u[i], 0x4B400000u, 0x7650)) - 12583040.0f;
+        f[4 * i + 1] = __uint_as_float(__byte_perm(u[i], 0x4B400000u, 0x7651)) - 12583040.0f;
+        f[4 * i + 2] = __uint_as_float(__byte_perm(u[i], 0x4B400000u, 0x7652)) - 12583040.0f;
+        f[4 * i + 3] = __uint_as_float(__byte_perm(u[i], 0x4B400000u, 0x7653)) - 12583040.0f;
     }
 }
 
