@@ -72,13 +72,17 @@ __device__ __forceinline__ int exp_int(int d) {
 // exp(-(mx - u)/256) with the difference clamped before subtracting (mx - u may not fit in int32)
 __device__ __forceinline__ int exp_dif(int mx, int u) { return exp_int(u <= mx - 6000 ? 6000 : mx - u); }
 
-// integer square root, 10 Newton steps from a power of two (ops.py:84-89)
+// integer square root (ops.py:84-89: 10 Newton steps from a power of two above the root, each min(x, (x + n/x) >> 1); from
+// above they converge to floor(sqrt(n)) well inside 10 steps for every n < 2^31, and the result is clamped to >= 1).
+// Here: the fp32 estimate is within 1 of the root (n has at most 31 bits, the estimate's error is far below 1), two integer
+// corrections make it exact.  r <= 46340, so r^2 and (r+1)^2 fit an unsigned 32-bit integer.
 __device__ __forceinline__ int isqrt_i(int n) {
     n = max(n, 0);
-    int x = 1 << ((bitlen(n) + 1) / 2);
-#pragma unroll
-    for (int i = 0; i < 10; i++) x = min(x, (x + n / max(x, 1)) >> 1);
-    return max(x, 1);
+    unsigned r = (unsigned)__float2int_rd(sqrtf((float)n));
+    r = min(r, 46340u);
+    if (r * r > (unsigned)n) r -= 1;
+    if ((r + 1) * (r + 1) <= (unsigned)n) r += 1;
+    return max((int)r, 1);
 }
 
 // ---------------------------------------------------------------------------------------- lane groups
