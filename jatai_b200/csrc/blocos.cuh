@@ -25,6 +25,30 @@ __global__ void __launch_bounds__(256) k_quant(const int* __restrict__ acc, cons
     int v[16], ee[16], q[16];
     le16_i32(acc + o, v);
     le16_i16(e + o, ee);
+    {
+        // fp32 path (a whole warp or none): every |v| <= 2^24 is exact in fp32, v * 2^(e - largest exponent of a non-zero value
+        // of the block) is an exact scaling while the exponents are at most 100 apart, and the fp32 quantiser then gives the
+        // bits of the integer one (the block's top bit and the one-more-bit retry depend on the largest scaled magnitude alone)
+        int eref = -32768, big = 0;
+#pragma unroll
+        for (int i = 0; i < 16; i++) {
+            big |= (v[i] > (1 << 24)) | (v[i] < -(1 << 24));
+            if (v[i] != 0) eref = max(eref, ee[i]);
+        }
+        eref = grupo_max<BLK / 16>(eref);
+#pragma unroll
+        for (int i = 0; i < 16; i++) big |= (v[i] != 0) & (eref - ee[i] > 100);
+        if (__all_sync(FULL, big == 0)) {
+            float f[16];
+#pragma unroll
+            for (int i = 0; i < 16; i++) f[i] = (float)v[i] * __int_as_float((127 + max(min(ee[i] - eref, 0), -100)) << 23);
+            uint4 pac;
+            const int Eo = quant_f32<BLK / 16>(f, eref, pac, kid, o);
+            if (ativo) *reinterpret_cast<uint4*>(m + o) = pac;
+            if (lider) E[w] = (int8_t)Eo;
+            return;
+        }
+    }
     // blocks whose elements all carry one exponent (attention outputs: one exponent per head) take the cheaper
     // uniform quantiser; the choice is made per block, the lanes of a block always agree
     int dif = 0;
