@@ -51,6 +51,10 @@ int jt_res_estocastico(int ligado);                        /* jatai_cuda.cu:1087
  * give-up path can be exercised with a short limit: *saiu (a device int) becomes 2 and the error record holds code 7,
  * place 99; the context stays usable. */
 int jt_espera_limite(long long ciclos);
+/* No counterpart in the reference.  1: the kernels of the training step are launched as programmatic dependent launches -
+ * each may be scheduled while its predecessor in the stream drains and waits (griddepcontrol.wait) before its first access
+ * to global memory; 0 (default): plain stream order.  Same results either way. */
+int jt_pdl(int ligado);
 int jt_teste_espera(int* saiu, int kid);
 
 /* ---- GEMM: C[M,N] = A[M,K] . B[N,K]^T, operands blocked along K ---------------------------------- */

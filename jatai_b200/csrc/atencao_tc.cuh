@@ -150,6 +150,8 @@ struct ArgsPrep {
 
 // grid (ceil(T / 128), BH, 4), 256 threads: 128 tokens of one head of one tensor
 __global__ void __launch_bounds__(256) k_at_prep(const ArgsPrep A) {
+    pdl_espera();
+    pdl_solta();
     __shared__ int red[8];
     __shared__ __align__(16) uint8_t tr[128 * 144];
     const int tid = threadIdx.x, z = blockIdx.z, bh = blockIdx.y, b = bh / A.H, h = bh % A.H, t0 = blockIdx.x * 128;
@@ -247,6 +249,10 @@ __global__ void __launch_bounds__(NTL) k_atencao_tc(const __grid_constant__ CUte
         for (int i = 0; i < 12; i++) mbar_init(bar[i], 1);
         *aborta = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    pdl_espera();                                                  // the operands below are the previous kernel's outputs
+    pdl_solta();
+    if (tid == 0) {
         mbar_expect_tx(bar[0], TILE_NI);
         tma_2d(sQ, &mQ, 0, bh * T + i0, bar[0]);
         for (int c = 0; c < NSTF && c < nvoltas; c++) {
@@ -486,6 +492,10 @@ __global__ void __launch_bounds__(NTL) k_ab_linhas_tc(const __grid_constant__ CU
         for (int i = 0; i < 14; i++) mbar_init(bar[i], 1);
         *aborta = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    pdl_espera();                                                  // the operands below are the previous kernel's outputs
+    pdl_solta();
+    if (tid == 0) {
         mbar_expect_tx(bar[0], TILE_NI);
         tma_2d(sG, &mG, 0, bh * T + i0, bar[0]);
         for (int c = 0; c < NSTV && c < nvoltas; c++) {
@@ -715,12 +725,15 @@ __global__ void __launch_bounds__(256) k_ab_colunas_tc(const __grid_constant__ C
         tma_2d(s + 2 * TILE_A + TILE_NJ, &mDl, ic, bh * T + j0, f);
         tma_2d(s + 2 * TILE_A + 2 * TILE_NJ, &mP, ic, bh * T + j0, f);
     };
-    if (tid == 0) {                                                // the loads go out before anything else
+    if (tid == 0) {
         for (int i = 0; i < 7; i++) mbar_init(bar[i], 1);
         *aborta = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        for (int c = 0; c < NSTC && c < nq; c++) carrega(c);
     }
+    pdl_espera();                                                  // the operands are the previous kernels' outputs
+    pdl_solta();
+    if (tid == 0)                                                  // the loads go out before anything else
+        for (int c = 0; c < NSTC && c < nq; c++) carrega(c);
     if (wid == 0) tmem_aloca(slot, 256);
     tc_fence_antes();
     __syncthreads();
@@ -812,14 +825,14 @@ static int atencao_frente_tc(int blk, const int8_t* qm, const int8_t* qE, int* O
     int* em = reinterpret_cast<int*>(ws);
     int8_t *Q2 = reinterpret_cast<int8_t*>(ws + b_em), *K2 = Q2 + b_lin, *Vt2 = K2 + b_lin;
     atc::ArgsPrep Pp = {qm, qE, nullptr, nullptr, {Q2, K2, nullptr, nullptr}, {nullptr, nullptr, Vt2, nullptr}, em, nullptr, T, H, D, GA, blk};
-    atc::k_at_prep<<<dim3((T + 127) / 128, BH, 3), 256, 0, st>>>(Pp);
+    lanca_pdl(atc::k_at_prep, dim3(dim3((T + 127) / 128, BH, 3)), dim3(256), 0, st, Pp);
     CUtensorMap mQ, mK, mVt;
     if (!(faz_mapa(&mQ, Q2, BH * T, 128, atc::NI) && faz_mapa(&mK, K2, BH * T, 128, 128) && faz_mapa(&mVt, Vt2, BH * 128, T, 128)))
         return (int)cudaErrorInvalidValue;
     const size_t sm = atc::smem_frente_tc(T);
     cudaError_t c = at_smem(atc::k_atencao_tc, sm);
     if (c != cudaSuccess) return (int)c;
-    atc::k_atencao_tc<<<dim3(T / atc::NI, BH), atc::NTL, sm, st>>>(mQ, mK, mVt, em, Oacc, Oe, Qm, QE, P, T, H, D, GA, kid);
+    lanca_pdl(atc::k_atencao_tc, dim3(dim3(T / atc::NI, BH)), dim3(atc::NTL), sm, st, mQ, mK, mVt, em, Oacc, Oe, Qm, QE, P, T, H, D, GA, kid);
     return (int)cudaGetLastError();
 }
 
@@ -839,7 +852,7 @@ static int atencao_tras_tc(int blk, const int8_t* gom, const int8_t* goE, const 
     int8_t *DSh = Gt2 + b_lin, *DSl = DSh + b_ds;
     cudaError_t c;
     atc::ArgsPrep Pp = {qm, qE, gom, goE, {nullptr, nullptr, V2, G2}, {Qt2, Kt2, nullptr, Gt2}, em, est, T, H, D, GA, blk};
-    atc::k_at_prep<<<dim3((T + 127) / 128, BH, 4), 256, 0, st>>>(Pp);
+    lanca_pdl(atc::k_at_prep, dim3(dim3((T + 127) / 128, BH, 4)), dim3(256), 0, st, Pp);
     CUtensorMap mV, mG, mKt, mQt, mGt, mDh, mDl, mP;
     if (!(faz_mapa(&mV, V2, BH * T, 128, 128) && faz_mapa(&mG, G2, BH * T, 128, atc::NI) && faz_mapa(&mKt, Kt2, BH * 128, T, 128) &&
           faz_mapa(&mQt, Qt2, BH * 128, T, 128) && faz_mapa(&mGt, Gt2, BH * 128, T, 128) && faz_mapa(&mDh, DSh, BH * T, T, atc::NJ) &&
@@ -852,14 +865,14 @@ static int atencao_tras_tc(int blk, const int8_t* gom, const int8_t* goE, const 
         at::k_lim<atc::HD><<<BH, 256, 0, st>>>(L);
     } else {
         if ((c = at_smem(atc::k_ab_linhas_tc<1>, atc::smem_linhas_tc(1))) != cudaSuccess) return (int)c;
-        atc::k_ab_linhas_tc<1><<<grade, atc::NTL, atc::smem_linhas_tc(1), st>>>(mV, mG, mKt, A);
+        lanca_pdl(atc::k_ab_linhas_tc<1>, dim3(grade), dim3(atc::NTL), atc::smem_linhas_tc(1), st, mV, mG, mKt, A);
     }
     if ((c = at_smem(atc::k_ab_linhas_tc<2>, atc::smem_linhas_tc(2))) != cudaSuccess) return (int)c;
-    atc::k_ab_linhas_tc<2><<<grade, atc::NTL, atc::smem_linhas_tc(2), st>>>(mV, mG, mKt, A);
+    lanca_pdl(atc::k_ab_linhas_tc<2>, dim3(grade), dim3(atc::NTL), atc::smem_linhas_tc(2), st, mV, mG, mKt, A);
     if ((c = at_smem(atc::k_ab_linhas_tc<3>, atc::smem_linhas_tc(3))) != cudaSuccess) return (int)c;
-    atc::k_ab_linhas_tc<3><<<grade, atc::NTL, atc::smem_linhas_tc(3), st>>>(mV, mG, mKt, A);
+    lanca_pdl(atc::k_ab_linhas_tc<3>, dim3(grade), dim3(atc::NTL), atc::smem_linhas_tc(3), st, mV, mG, mKt, A);
     if ((c = at_smem(atc::k_ab_colunas_tc, atc::smem_colunas_tc())) != cudaSuccess) return (int)c;
-    atc::k_ab_colunas_tc<<<dim3((T + atc::NJ - 1) / atc::NJ, BH), 256, atc::smem_colunas_tc(), st>>>(mQt, mGt, mDh, mDl, mP, A);
+    lanca_pdl(atc::k_ab_colunas_tc, dim3(dim3((T + atc::NJ - 1) / atc::NJ, BH)), dim3(256), atc::smem_colunas_tc(), st, mQt, mGt, mDh, mDl, mP, A);
     return (int)cudaGetLastError();
 }
 

@@ -295,6 +295,8 @@ template <int BLK>
 __global__ void __launch_bounds__(256) k_momento_peso(const int* __restrict__ gacc, const int16_t* __restrict__ ge, int8_t* __restrict__ Mm,
                                                       int8_t* __restrict__ ME, int8_t* __restrict__ Wm, int8_t* __restrict__ WE,
                                                       int8_t* __restrict__ Rm, int8_t* __restrict__ RE, int k_lr, int ef, long long n16, int kid) {
+    pdl_espera();
+    pdl_solta();
     JT_FIO16
     int mv[16], Em;
     {
@@ -342,6 +344,8 @@ __global__ void __launch_bounds__(256) k_momento_peso(const int* __restrict__ ga
 template <int BLK>
 __global__ void __launch_bounds__(256) k_embed(const int8_t* __restrict__ Wm, const int8_t* __restrict__ WE, const int* __restrict__ tok,
                                                int8_t* __restrict__ Xm, int8_t* __restrict__ XE, int M, int D, int V, int kid) {
+    pdl_espera();
+    pdl_solta();
     const int por_linha = D / 16;
     const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (t >= (long long)M * por_linha) return;
@@ -359,6 +363,8 @@ __global__ void __launch_bounds__(256) k_embed(const int8_t* __restrict__ Wm, co
 template <int BLK>
 __global__ void __launch_bounds__(256) k_um_quente(const int* __restrict__ tok, int8_t* __restrict__ U, int8_t* __restrict__ UE, int M, int V,
                                                    int kid) {
+    pdl_espera();
+    pdl_solta();
     const int por_linha = V / 16;
     const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (t >= (long long)M * por_linha) return;
@@ -453,6 +459,8 @@ __device__ __forceinline__ void max4_atomico(int8_t* p, uint32_t meu) {
 template <int TR, int CPT>
 __device__ __forceinline__ void transpoe32_corpo(const int8_t* __restrict__ X, const int8_t* __restrict__ EX, int8_t* __restrict__ Y,
                                                  int8_t* __restrict__ EY, int R, int C, int kid, int8_t* __restrict__ RM = nullptr) {
+    pdl_espera();
+    pdl_solta();
     static_assert(CPT == 4 || CPT == 1, "a thread owns the 4 columns of a word or one of them");
     constexpr int TC = 256, PW = T32_PW, NT = 8 * TR / CPT, NPAR = (TR / 32) * 8;
     __shared__ uint32_t tile[TR][PW];
@@ -555,6 +563,8 @@ template <int BLK, int NP>
 __global__ void __launch_bounds__(256) k_rms(const int8_t* __restrict__ Xm, const int8_t* __restrict__ XE, int8_t* __restrict__ Ym,
                                              int8_t* __restrict__ YE, int* __restrict__ cr, int* __restrict__ cemax, int M, int D, int log2D, int G,
                                              int kid) {
+    pdl_espera();
+    pdl_solta();
     constexpr int GL = BLK / 16;
     const int lane = threadIdx.x & 31;
     const long long lin_ = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
@@ -617,6 +627,8 @@ __device__ __forceinline__ void rms_back_corpo(const int8_t* __restrict__ gm, co
                                                const int8_t* __restrict__ yE, const int* __restrict__ cr, const int* __restrict__ cemax,
                                                const int8_t* __restrict__ xm, const int8_t* __restrict__ xE, int8_t* __restrict__ om,
                                                int8_t* __restrict__ oE, int M, int D, int log2D, int G, int GB, int kid) {
+    pdl_espera();
+    pdl_solta();
     constexpr int GL = BLK / 16;
     const int lane = threadIdx.x & 31;
     const long long lin_ = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
@@ -709,6 +721,8 @@ template <int BLK, int NP>
 __global__ void __launch_bounds__(256) k_softmax_ce(const int* __restrict__ acc, const int16_t* __restrict__ e, const int* __restrict__ alvo,
                                                     int8_t* __restrict__ gm, int8_t* __restrict__ gE, int* __restrict__ d_alvo, int* __restrict__ soma,
                                                     int M, int V, int log2M, int kid) {
+    pdl_espera();
+    pdl_solta();
     constexpr int GL = BLK / 16;
     const int lane = threadIdx.x & 31;
     const long long lin_ = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);

@@ -247,6 +247,8 @@ __global__ void __launch_bounds__(Cfg<TNv, VIA>::N_THR, Cfg<TNv, VIA>::CTAS_SM) 
     __syncthreads();
     tc_fence_depois();
     const uint32_t tmem = *tmem_slot;
+    pdl_espera();                                  // everything above touches no global memory: it overlaps the predecessor's tail
+    pdl_solta();
 
     if (wid == 0) {
         // ------------------------------------------------------------------ TMA producer + column scale tables

@@ -55,7 +55,7 @@ static int lanca_tc(const CUtensorMap& mA, const CUtensorMap& mB, const int8_t* 
         pronto = true;
     }
     const dim3 grade(N / TNv, M / tc::TM, partes);
-    k<<<grade, C_::N_THR, C_::SMEM_BYTES, g_stream>>>(mA, mB, EA, EB, RA, RB, S, M, N, K, (K / tc::KC) / partes, kid);
+    lanca_pdl(k, grade, dim3(C_::N_THR), C_::SMEM_BYTES, g_stream, mA, mB, EA, EB, RA, RB, S, M, N, K, (K / tc::KC) / partes, kid);
     return fim();
 }
 
@@ -139,6 +139,8 @@ int jt_teste_espera(int* saiu, int kid) {
     tc::k_teste_espera<<<1, 32, 0, g_stream>>>(kid, saiu);
     return fim();
 }
+// Programmatic dependent launch of the kernels that support it (0 = plain stream order).
+int jt_pdl(int ligado) { pdl_ligado() = ligado ? 1 : 0; return 0; }
 int jt_erro_limpa() {
     Erro e;
     memset(&e, 0, sizeof(e));
@@ -242,8 +244,8 @@ int jt_momento_peso(const void* gacc, const void* ge, void* Mm, void* ME, void* 
                     long long nblocos, int kid) {
     const long long n16 = JT_N16;
 #define ARGS (const int*)gacc, (const int16_t*)ge, (int8_t*)Mm, (int8_t*)ME, (int8_t*)Wm, (int8_t*)WE, (int8_t*)Rm, (int8_t*)RE, k_lr, ef, n16, kid
-    if (g_blk == 32) k_momento_peso<32><<<nblocos16(n16), 256, 0, g_stream>>>(ARGS);
-    else k_momento_peso<128><<<nblocos16(n16), 256, 0, g_stream>>>(ARGS);
+    if (g_blk == 32) lanca_pdl(k_momento_peso<32>, dim3(nblocos16(n16)), dim3(256), 0, g_stream, ARGS);
+    else lanca_pdl(k_momento_peso<128>, dim3(nblocos16(n16)), dim3(256), 0, g_stream, ARGS);
 #undef ARGS
     return fim();
 }
@@ -252,10 +254,10 @@ int jt_transpoe(const void* X, const void* EX, void* Y, void* EY, int R, int C, 
     if (g_blk == 32 && C % 256 == 0 && ((uintptr_t)EX & 3) == 0) {
         const long long t128 = (long long)(C / 256) * (R / 128);
 #define ARGS (const int8_t*)X, (const int8_t*)EX, (int8_t*)Y, (int8_t*)EY, R, C, kid
-        if (t128 >= 148) k_transpoe32<128><<<dim3(C / 256, R / 128), 256, 0, g_stream>>>(ARGS);
-        else if (2 * t128 >= 148) k_transpoe32<64><<<dim3(C / 256, R / 64), 128, 0, g_stream>>>(ARGS);
-        else if (4 * t128 >= 296) k_transpoe32<32><<<dim3(C / 256, R / 32), 64, 0, g_stream>>>(ARGS);
-        else k_transpoe32<32, 1><<<dim3(C / 256, R / 32), 256, 0, g_stream>>>(ARGS);
+        if (t128 >= 148) lanca_pdl(k_transpoe32<128>, dim3(dim3(C / 256, R / 128)), dim3(256), 0, g_stream, ARGS);
+        else if (2 * t128 >= 148) lanca_pdl(k_transpoe32<64>, dim3(dim3(C / 256, R / 64)), dim3(128), 0, g_stream, ARGS);
+        else if (4 * t128 >= 296) lanca_pdl(k_transpoe32<32>, dim3(dim3(C / 256, R / 32)), dim3(64), 0, g_stream, ARGS);
+        else lanca_pdl(k_transpoe32<32, 1>, dim3(dim3(C / 256, R / 32)), dim3(256), 0, g_stream, ARGS);
 #undef ARGS
         return fim();
     }
@@ -276,10 +278,10 @@ static int transpoe2_impl(const void* X1, const void* EX1, void* Y1, void* EY1, 
         const ArgsTransp a1 = {(const int8_t*)X2, (const int8_t*)EX2, (int8_t*)Y2, (int8_t*)EY2, C2, (int8_t*)RM2};
         const int cx = (C1 > C2 ? C1 : C2) / 256;
         const long long t128 = (long long)((C1 + C2) / 256) * (R / 128);
-        if (t128 >= 148) k_transpoe32_par<128><<<dim3(cx, R / 128, 2), 256, 0, g_stream>>>(a0, a1, R, kid);
-        else if (2 * t128 >= 148) k_transpoe32_par<64><<<dim3(cx, R / 64, 2), 128, 0, g_stream>>>(a0, a1, R, kid);
-        else if (4 * t128 >= 296) k_transpoe32_par<32><<<dim3(cx, R / 32, 2), 64, 0, g_stream>>>(a0, a1, R, kid);
-        else k_transpoe32_par<32, 1><<<dim3(cx, R / 32, 2), 256, 0, g_stream>>>(a0, a1, R, kid);
+        if (t128 >= 148) lanca_pdl(k_transpoe32_par<128>, dim3(dim3(cx, R / 128, 2)), dim3(256), 0, g_stream, a0, a1, R, kid);
+        else if (2 * t128 >= 148) lanca_pdl(k_transpoe32_par<64>, dim3(dim3(cx, R / 64, 2)), dim3(128), 0, g_stream, a0, a1, R, kid);
+        else if (4 * t128 >= 296) lanca_pdl(k_transpoe32_par<32>, dim3(dim3(cx, R / 32, 2)), dim3(64), 0, g_stream, a0, a1, R, kid);
+        else lanca_pdl(k_transpoe32_par<32, 1>, dim3(dim3(cx, R / 32, 2)), dim3(256), 0, g_stream, a0, a1, R, kid);
         return fim();
     }
     if (com_max) return (int)cudaErrorNotSupported;            // the maxima are written by the wide block-32 kernel only
@@ -299,16 +301,16 @@ int jt_embed(const void* Wm, const void* WE, const void* tok, void* Xm, void* XE
     if (M <= 0 || D <= 0 || D % g_blk) return (int)cudaErrorInvalidValue;
     const unsigned g = (unsigned)(((long long)M * (D / 16) + 255) / 256);
 #define ARGS (const int8_t*)Wm, (const int8_t*)WE, (const int*)tok, (int8_t*)Xm, (int8_t*)XE, M, D, V, kid
-    if (g_blk == 32) k_embed<32><<<g, 256, 0, g_stream>>>(ARGS);
-    else k_embed<128><<<g, 256, 0, g_stream>>>(ARGS);
+    if (g_blk == 32) lanca_pdl(k_embed<32>, dim3(g), dim3(256), 0, g_stream, ARGS);
+    else lanca_pdl(k_embed<128>, dim3(g), dim3(256), 0, g_stream, ARGS);
 #undef ARGS
     return fim();
 }
 int jt_um_quente(const void* tok, void* U, void* UE, int M, int V, int kid) {
     if (M <= 0 || V <= 0 || V % g_blk) return (int)cudaErrorInvalidValue;
     const unsigned g = (unsigned)(((long long)M * (V / 16) + 255) / 256);
-    if (g_blk == 32) k_um_quente<32><<<g, 256, 0, g_stream>>>((const int*)tok, (int8_t*)U, (int8_t*)UE, M, V, kid);
-    else k_um_quente<128><<<g, 256, 0, g_stream>>>((const int*)tok, (int8_t*)U, (int8_t*)UE, M, V, kid);
+    if (g_blk == 32) lanca_pdl(k_um_quente<32>, dim3(g), dim3(256), 0, g_stream, (const int*)tok, (int8_t*)U, (int8_t*)UE, M, V, kid);
+    else lanca_pdl(k_um_quente<128>, dim3(g), dim3(256), 0, g_stream, (const int*)tok, (int8_t*)U, (int8_t*)UE, M, V, kid);
     return fim();
 }
 
@@ -318,13 +320,13 @@ int jt_um_quente(const void* tok, void* U, void* UE, int M, int V, int kid) {
         const unsigned g_ = (unsigned)((M + 7) / 8);                                                 \
         const int np_ = ((COLS) + 511) / 512;                                                        \
         if (g_blk == 32) {                                                                           \
-            if (np_ == 1) KERN<32, 1><<<g_, 256, 0, g_stream>>>(__VA_ARGS__);                        \
-            else if (np_ == 2) KERN<32, 2><<<g_, 256, 0, g_stream>>>(__VA_ARGS__);                   \
-            else KERN<32, 4><<<g_, 256, 0, g_stream>>>(__VA_ARGS__);                                 \
+            if (np_ == 1) lanca_pdl(KERN<32, 1>, dim3(g_), dim3(256), 0, g_stream, __VA_ARGS__);                        \
+            else if (np_ == 2) lanca_pdl(KERN<32, 2>, dim3(g_), dim3(256), 0, g_stream, __VA_ARGS__);                   \
+            else lanca_pdl(KERN<32, 4>, dim3(g_), dim3(256), 0, g_stream, __VA_ARGS__);                                 \
         } else {                                                                                     \
-            if (np_ == 1) KERN<128, 1><<<g_, 256, 0, g_stream>>>(__VA_ARGS__);                       \
-            else if (np_ == 2) KERN<128, 2><<<g_, 256, 0, g_stream>>>(__VA_ARGS__);                  \
-            else KERN<128, 4><<<g_, 256, 0, g_stream>>>(__VA_ARGS__);                                \
+            if (np_ == 1) lanca_pdl(KERN<128, 1>, dim3(g_), dim3(256), 0, g_stream, __VA_ARGS__);                       \
+            else if (np_ == 2) lanca_pdl(KERN<128, 2>, dim3(g_), dim3(256), 0, g_stream, __VA_ARGS__);                  \
+            else lanca_pdl(KERN<128, 4>, dim3(g_), dim3(256), 0, g_stream, __VA_ARGS__);                                \
         }                                                                                            \
     } while (0)
 
