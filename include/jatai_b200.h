@@ -56,6 +56,10 @@ int jt_espera_limite(long long ciclos);
  * to global memory; 0 (default): plain stream order.  Same results either way. */
 int jt_pdl(int ligado);
 int jt_teste_espera(int* saiu, int kid);
+/* Test switch, no counterpart in the reference: 1 = the tensor-core GEMM issues no operand load; its first in-kernel wait
+ * then runs out after the limit in force with no copy or MMA in flight, every warp leaves through the abort path, the
+ * launch returns with code 7 recorded (outputs undefined).  0 = normal. */
+int jt_gemm_sem_cargas(int ligado);
 
 /* ---- GEMM: C[M,N] = A[M,K] . B[N,K]^T, operands blocked along K ---------------------------------- */
 /* modo 0 block output (Cm, CE) | 1 raw output (C32, Ce) | 2 block + residual add of X | 3 block h and

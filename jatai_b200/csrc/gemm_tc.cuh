@@ -55,6 +55,8 @@ struct Cfg {
 };
 constexpr long long LIMITE_CICLOS = 4000000000LL;              // ~2 s at B200 clocks
 __device__ long long g_limite_espera = LIMITE_CICLOS;          // the limit in force (jt_espera_limite); read on the slow path of a wait only
+__device__ int g_sem_cargas = 0;                               // test switch (jt_gemm_sem_cargas): the producer issues no operand load, so the
+                                                               // first wait of the MMA warp runs out with nothing asynchronous in flight
 constexpr uint32_t MAGIA = 0x4B400000u;                        // bit pattern of 1.5 * 2^23
 constexpr float MAGIA_F = 12582912.0f;
 constexpr int DESLOC = 32 * 127 * 127;                         // the largest |partial product| of 32 int8 pairs
@@ -262,7 +264,8 @@ __global__ void __launch_bounds__(Cfg<TNv, VIA>::N_THR, Cfg<TNv, VIA>::CTAS_SM) 
         };
         // the first NST stages are free: their loads start before anything else, the row maxima (computed by the
         // drain threads meanwhile) are only needed for the scale tables
-        if (lane == 0)
+        const bool sem_cargas = *reinterpret_cast<volatile int*>(&g_sem_cargas) != 0;
+        if (lane == 0 && !sem_cargas)
             for (int i = 0; i < NST && i < pedacos_por_parte; i++) carrega(i);
         const int8_t* ebc[NC];
         uint32_t w[NC];                           // block exponents of this lane's columns for the next chunk, read one chunk ahead
@@ -283,7 +286,7 @@ __global__ void __launch_bounds__(Cfg<TNv, VIA>::N_THR, Cfg<TNv, VIA>::CTAS_SM) 
         for (int i = 0; i < pedacos_por_parte; i++) {
             if (lane == 0 && i >= NST) {
                 ok = espera(bar_empty + 8 * (i % NST), ((i / NST) & 1) ^ 1, aborta, kid, 1);
-                if (ok) carrega(i);
+                if (ok && !sem_cargas) carrega(i);
             }
             ok = __all_sync(FULL, ok);
             if (!ok) break;

@@ -133,6 +133,12 @@ int jt_espera_limite(long long ciclos) {
     const long long v = ciclos > 0 ? ciclos : tc::LIMITE_CICLOS;
     return (int)cudaMemcpyToSymbol(tc::g_limite_espera, &v, sizeof(v));
 }
+// Test switch: with 1 the tensor-core GEMM issues no operand load, so its MMA warp's first wait runs out after the limit in
+// force, the CTA records code 7, raises its abort flag and every warp leaves through the normal exit (outputs undefined).
+int jt_gemm_sem_cargas(int ligado) {
+    const int v = ligado ? 1 : 0;
+    return (int)cudaMemcpyToSymbol(tc::g_sem_cargas, &v, sizeof(v));
+}
 // Self-test of the bounded wait: one warp waits on a barrier nothing completes and must give up after the limit in force
 // (set a short one first).  *saiu (device int) becomes 2 when it gave up; the error record then holds code 7, place 99.
 int jt_teste_espera(int* saiu, int kid) {

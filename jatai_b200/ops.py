@@ -32,7 +32,7 @@ _INT_FUNCS = ("jt_gemm", "jt_gemm_f", "jt_gemm_ext", "jt_max_linha", "jt_quant",
               "jt_momento", "jt_peso", "jt_momento_peso", "jt_transpoe", "jt_transpoe2", "jt_embed", "jt_um_quente", "jt_rms", "jt_rms_back", "jt_rms_back_soma", "jt_atencao",
               "jt_atencao_back", "jt_softmax_ce", "jt_erro_le", "jt_erro_limpa", "jt_sincroniza", "jt_para16", "jt_para8",
               "jt_soma16", "jt_res_estocastico", "jt_blk", "jt_blk_atual", "jt_gemm_via", "jt_gemm_tn", "jt_atencao_back_fixo", "jt_atencao_via", "jt_atencao_quant", "jt_atencao_back_quant",
-              "jt_espera_limite", "jt_teste_espera", "jt_transpoe2_max", "jt_pdl")
+              "jt_espera_limite", "jt_teste_espera", "jt_transpoe2_max", "jt_pdl", "jt_gemm_sem_cargas")
 
 
 def g_rms(D):

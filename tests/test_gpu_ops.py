@@ -533,3 +533,42 @@ def test_transpoe_par_com_maximos(amb, R, C1, C2, esp):
     assert torch.equal(buf[256:256 + C1], r1) and torch.equal(buf[256 + C1:], r2)
     assert bool((buf[:256] == -128).all())
     assert oc.transpoe2_max(para_gpu(G.bloco(128, 192, espalha=2, zera=0.0)), para_gpu(G.bloco(128, 256, espalha=2, zera=0.0)), buf[:192], buf[256:512]) is None
+
+
+@pytest.mark.gpu
+def test_gemm_abandona_uma_espera_e_o_seguinte_e_exato(amb):
+    """The abort path of the tensor-core GEMM itself: with its operand loads switched off (nothing asynchronous in flight) and
+    the wait limit shortened, the MMA warp's first wait runs out, the CTAs record code 7 with the launch id of that GEMM,
+    every warp leaves through the normal exit and the launch returns; the next GEMM is bit-exact."""
+    import ctypes
+    import json
+    import time
+    ops, oc, reg = amb
+    lib = oc.lib
+    ops.define_blk(32)
+    X, W, _ = (para_gpu(t) for t in casos.config1(32))
+    torch.cuda.synchronize()
+    assert lib.jt_erro_limpa() == 0
+    vigiar, reg.vigiar = reg.vigiar, False                       # the registry would raise on the record this test provokes
+    assert lib.jt_espera_limite(ctypes.c_longlong(2_000_000)) == 0 and lib.jt_gemm_sem_cargas(1) == 0
+    try:
+        reg.novo_passo(0)
+        t0 = time.time()
+        oc.gemm(X, W)
+        kid = len(reg.lancamentos) - 1
+        torch.cuda.synchronize()
+        dt = time.time() - t0
+        out = (ctypes.c_longlong * 6)()
+        n = lib.jt_erro_le(out)
+        assert n >= 1 and out[1] == 7 and out[2] == kid, list(out)
+        assert dt < 5.0, f"the aborted GEMM took {dt:.2f} s with a limit of about 1 ms"
+    finally:
+        assert lib.jt_gemm_sem_cargas(0) == 0 and lib.jt_espera_limite(ctypes.c_longlong(0)) == 0
+        assert lib.jt_erro_limpa() == 0
+        reg.vigiar = vigiar
+    reg.novo_passo(0)
+    with open(os.path.join(gu.AQUI, "config1_b32.json")) as fh:
+        rec = json.load(fh)
+    Y = oc.gemm(X, W)
+    torch.cuda.synchronize()
+    assert [gu.digest(t) for t in Y] == rec["Y"]
