@@ -54,6 +54,30 @@ def test_retomar_continua_bit_a_bit():
         assert torch.equal(x, y), f"state tensor {i} differs after resume"
 
 
+def test_restaura_le_o_arquivo_de_pesos_da_referencia():
+    """The reference's weight file (noite.py:88-91: modo, L, FF, pesos, residuo) loads: weights and residual as stored, momentum
+    from zero, step 0, with a warning that the continuation is not bit-exact; a file for another depth is refused."""
+    import pytest
+    from jatai_b200 import dados, estado, ops
+    fonte = dados.sintetico(3000, 5) % 128
+    a, ga = _modelo(), torch.Generator().manual_seed(1)
+    for _ in range(2):
+        a.passo(*dados.lote(fonte, ga, 2, 32), k_lr=4)
+    arq = os.path.join(tempfile.mkdtemp(), "ref_pesos.pt")
+    torch.save({"modo": "int8", "L": a.L, "FF": a.FF, "pesos": {k: (m.cpu(), e.cpu()) for k, (m, e) in a.p.items()},
+                "residuo": {k: (m.cpu(), e.cpu()) for k, (m, e) in a.res.items()}}, arq)
+    b = _modelo()
+    with pytest.warns(UserWarning, match="not bit-exact"):
+        assert estado.restaura(b, arq) == 0
+    for n in a.p:
+        assert all(torch.equal(x, y) for x, y in zip(a.p[n], b.p[n])) and all(torch.equal(x, y) for x, y in zip(a.res[n], b.res[n]))
+        assert int(b.mom[n][0].abs().max()) == 0 and bool((b.mom[n][1] == ops.E_ZERO).all())
+    b.passo(*dados.lote(fonte, ga, 2, 32), k_lr=4)                # and the model trains on from there
+    torch.save({"modo": "int8", "L": a.L + 1, "FF": a.FF, "pesos": {}, "residuo": {}}, arq)
+    with pytest.raises(ValueError):
+        estado.restaura(_modelo(), arq)
+
+
 def test_corpus_no_dispositivo_corta_os_mesmos_lotes():
     """The device-resident corpus draws the windows of the plain loader (same generator, same batches)."""
     from jatai_b200 import dados
