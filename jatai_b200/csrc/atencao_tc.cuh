@@ -145,6 +145,7 @@ struct ArgsPrep {
     int8_t* lin[4]; int8_t* tra[4];
     int* em;                    // [BH][4] head-maximum exponents, indexed by z
     int* est;                   // backward: the statistics slots [BH][N_EST] to clear (nullptr in the forward)
+    int* nrm;                   // forward: [BH][2][ceil(T/128)] largest sum of squares of an aligned row of q (0) / k (1) per 128 tokens, or nullptr
     int T, H, D, GA, blk;
 };
 
@@ -166,6 +167,7 @@ __global__ void __launch_bounds__(256) k_at_prep(const ArgsPrep A) {
     if (blockIdx.x == 0 && tid == 0) A.em[bh * 4 + z] = em;
     if (A.est && blockIdx.x == 0 && z == 3 && tid < at::N_EST) A.est[bh * at::N_EST + tid] = 0;
     const int r = tid >> 1, meio = tid & 1, t = t0 + r;
+    int norma = 0;
     if (t < T) {
         const size_t lin = (size_t)(linha0 + t);
 #pragma unroll
@@ -175,7 +177,11 @@ __global__ void __launch_bounds__(256) k_at_prep(const ArgsPrep A) {
             le16(m + lin * ld + col0 + c, v);
             const int s = em - (int)E[lin * ldb + (col0 + c) / blk];
 #pragma unroll
-            for (int k = 0; k < 16; k++) digitos(rnd_d(v[k] << A.GA, s), hi[k], lo[k]);
+            for (int k = 0; k < 16; k++) {
+                const int a = rnd_d(v[k] << A.GA, s);
+                norma += a * a;                                    // 12-bit values, 64 of them: below 2^28
+                digitos(a, hi[k], lo[k]);
+            }
             if (dl) {
                 int8_t* p = dl + ((size_t)bh * T + t) * 128 + c;
                 grava16(p, hi);
@@ -188,6 +194,19 @@ __global__ void __launch_bounds__(256) k_at_prep(const ArgsPrep A) {
                     tr[(64 + c + k) * 144 + r] = (uint8_t)lo[k];
                 }
             }
+        }
+    }
+    if (A.nrm && z < 2) {
+        // the largest squared norm of an aligned row among this CTA's 128 tokens (the two halves of a row sit in neighbouring lanes)
+        norma += __shfl_xor_sync(0xffffffffu, norma, 1);
+        norma = __reduce_max_sync(0xffffffffu, norma);
+        __syncthreads();                                           // red[] is free again (max_cabeca used it)
+        if ((tid & 31) == 0) red[tid >> 5] = norma;
+        __syncthreads();
+        if (tid == 0) {
+            int mx = 0;
+            for (int w = 0; w < 8; w++) mx = max(mx, red[w]);
+            A.nrm[((size_t)bh * 2 + z) * gridDim.x + blockIdx.x] = mx;
         }
     }
     if (dt) {
@@ -241,7 +260,7 @@ __global__ void __launch_bounds__(NTL) k_atencao_tc(const __grid_constant__ CUte
     const int tid = threadIdx.x, wid = tid >> 5, lane = tid & 31;
     const int ordem = blockIdx.y * gridDim.x + blockIdx.x;         // heaviest (last) row tiles of all heads first
     const int bh = ordem % gridDim.y, b = bh / H, h = bh % H, i0 = (gridDim.x - 1 - ordem / gridDim.y) * NI, linha0 = b * T;
-    const int nproc = i0 + NI, nch = (nproc + TJ - 1) / TJ, nvoltas = 2 * nch;
+    const int nproc = i0 + NI, nch = (nproc + TJ - 1) / TJ;
     const uint32_t sA[NSTF] = {sbase, sbase + TILE_A, sbase + 2 * TILE_A}, sQ = sbase + OFF_Q, sQ3 = sbase + OFF_Q3, sPB = sbase + OFF_PB;
     // a CTA lives a few microseconds, so what it waits for first is asked for first: the operand loads go out as soon as their
     // barriers exist, the small global reads follow, and tensor memory is allocated while all of that is in flight
@@ -255,19 +274,37 @@ __global__ void __launch_bounds__(NTL) k_atencao_tc(const __grid_constant__ CUte
     if (tid == 0) {
         mbar_expect_tx(bar[0], TILE_NI);
         tma_2d(sQ, &mQ, 0, bh * T + i0, bar[0]);
-        for (int c = 0; c < NSTF && c < nvoltas; c++) {
-            mbar_expect_tx(bar[B_K + c], TILE_A);
-            tma_2d(sA[c], &mK, 0, bh * T + (c % nch) * TJ, bar[B_K + c]);
-        }
     }
     const int emq = em[bh * 4], emk = em[bh * 4 + 1], emv = em[bh * 4 + 2];
+    const int s_u = -((emq - GA) + (emk - GA) - 3 + 8), incl = at::incl_alibi(h);
+    // Key chunks that cannot matter.  |q_i . k_j| <= sqrt(|q_i|^2 |k_j|^2) (the preparation left the largest squared norms per 128
+    // tokens), so with B >= (|x| >> s_u) + 1 every score is u_ij <= B - (i - j) 2^incl and every row maximum is m_i >= u_ii >= -B.
+    // The exponential (>> 3) is exactly 0 from m - u = 2130 on (p < 2^15 shifted by n + 3 >= 15), so a key at distance
+    // (i - j) 2^incl >= 2132 + 2 B adds nothing to the row sum, cannot be the maximum and has P = 0: chunks wholly at that distance
+    // from the tile's first query are left out of all three passes (P = 0 is still written).  Only on the right-shift path.
+    int c0 = 0;
+    if (s_u > 0 && s_u < 31) {
+        const int* nrm = em + 4 * gridDim.y;
+        const int nq = nrm[((size_t)bh * 2) * nchT + i0 / TJ];
+        int nk = 0;
+        for (int c = 0; c < nch; c++) nk = max(nk, nrm[((size_t)bh * 2 + 1) * nchT + c]);
+        const long long B = ((long long)sqrt((double)nq * (double)nk) + 2) >> s_u;
+        const long long lim = 2132 + 2 * (B + 2), D0 = (lim + (1 << incl) - 1) >> incl;
+        if (i0 - D0 + 1 > 0) c0 = (int)((i0 - D0 + 1) / TJ);
+    }
+    const int nviv = nch - c0, nvoltas = 2 * nviv;                  // live chunks c0 .. nch - 1, swept twice
+    if (tid == 0) {
+        for (int c = 0; c < NSTF && c < nvoltas; c++) {
+            mbar_expect_tx(bar[B_K + c], TILE_A);
+            tma_2d(sA[c], &mK, 0, bh * T + (c0 + c % nviv) * TJ, bar[B_K + c]);
+        }
+    }
     if (tid < NI) { m_s[tid] = U_MIN; s_acc[tid] = 0; }
     if (wid == 0) tmem_aloca(slot, 512);
     tc_fence_antes();
     __syncthreads();
     tc_fence_depois();
     const uint32_t tmem = *slot;
-    const int s_u = -((emq - GA) + (emk - GA) - 3 + 8), incl = at::incl_alibi(h);
     const int jl = 32 * (wid & 3) + lane, g = wid >> 2;            // this thread's key within a chunk, its quarter of the query rows
     const uint32_t t_lane = tmem + ((uint32_t)(32 * (wid & 3)) << 16);
 
@@ -287,16 +324,16 @@ __global__ void __launch_bounds__(NTL) k_atencao_tc(const __grid_constant__ CUte
     __syncthreads();
     if (tid == 0 && ok) ok = emite(0);
     for (int cc = 0; cc < nvoltas; cc++) {
-        const int c = cc % nch, st = cc & 1;
+        const int c = c0 + cc % nviv, st = cc & 1;
         if (tid == 0 && ok && cc + 1 < nvoltas) ok = emite(cc + 1);
         __syncwarp();
         ok = __all_sync(FULL, ok && espera(bar[B_S + st], (cc >> 1) & 1, aborta, kid, 22));
         tc_fence_depois();
         if (tid == 0 && ok && cc + NSTF < nvoltas) {               // this step's MMAs are done: its stage takes the chunk of step cc + 3
             mbar_expect_tx(bar[B_K + cc % NSTF], TILE_A);
-            tma_2d(sA[cc % NSTF], &mK, 0, bh * T + ((cc + NSTF) % nch) * TJ, bar[B_K + cc % NSTF]);
+            tma_2d(sA[cc % NSTF], &mK, 0, bh * T + (c0 + (cc + NSTF) % nviv) * TJ, bar[B_K + cc % NSTF]);
         }
-        if (cc == nch) {
+        if (cc == nviv) {
             // between the sweeps: the row maxima from the per-thread maxima
 #pragma unroll
             for (int k = 0; k < 16; k++) {
@@ -325,7 +362,7 @@ __global__ void __launch_bounds__(NTL) k_atencao_tc(const __grid_constant__ CUte
                     int u = (x + meio + ((x >> s_u) & 1)) >> s_u;
                     u += (dj + k) * menos;
                     const bool dentro = !diagonal || dj + k >= 0;
-                    if (cc < nch) v16[k] = max(v16[k], dentro ? u : U_MIN);
+                    if (cc < nviv) v16[k] = max(v16[k], dentro ? u : U_MIN);
                     else {
                         // a key beyond the diagonal counts as infinitely far below the maximum; mi >= u otherwise, and
                         // |u| < 2^30 + 2^18: the difference cannot overflow
@@ -347,7 +384,7 @@ __global__ void __launch_bounds__(NTL) k_atencao_tc(const __grid_constant__ CUte
                     const bool dentro = j <= i;
                     int u = U_MIN;
                     if (dentro) u = rnd(junta3(hh[k], cr[k], ll[k]), s_u, kid, (long long)(linha0 + i) * D + h * HD) - ((i - j) << incl);
-                    if (cc < nch) v16[k] = max(v16[k], u);
+                    if (cc < nviv) v16[k] = max(v16[k], u);
                     else {
                         const int ex = dentro ? exp_dif(mi[k], u) >> 3 : 0;
                         v16[k] += ex;
@@ -374,23 +411,24 @@ __global__ void __launch_bounds__(NTL) k_atencao_tc(const __grid_constant__ CUte
     __syncthreads();
 #pragma unroll
     for (int k = 0; k < 16; k++) mi[k] = m_s[16 * g + k];
-    // pass 3: P of every key (explicit zeros beyond the diagonal, to the end of the sequence) and O^T += V^T . P^T behind it
+    // pass 3: P of every key (explicit zeros before the first live chunk and beyond the diagonal, to the end of the sequence) and
+    // O^T += V^T . P^T behind it, over the live chunks (m = c - c0 counts them: stages and parities go by m)
     if (tid == 0 && ok) {
-        for (int c = 0; c < NSTF && c < nch; c++) {
-            mbar_expect_tx(bar[B_V + c], TILE_A);
-            tma_2d(sA[c], &mVt, c * TJ, bh * 128, bar[B_V + c]);
+        for (int m = 0; m < NSTF && m < nviv; m++) {
+            mbar_expect_tx(bar[B_V + m], TILE_A);
+            tma_2d(sA[m], &mVt, (c0 + m) * TJ, bh * 128, bar[B_V + m]);
         }
     }
     for (int c = 0; c < nchT; c++) {
-        const int st = c & 1, j = c * TJ + jl;
-        const bool com_mma = c < nch;
-        if (com_mma && c >= 2) ok = __all_sync(FULL, ok && espera(bar[B_PV + st], ((c - 2) >> 1) & 1, aborta, kid, 26));      // tile st is free again
-        if (com_mma && c >= 2 && c + 1 >= NSTF && c + 1 < nch && tid == 0 && ok) {      // and so is the operand stage of chunk c - 2: it takes chunk c + 1
-            mbar_expect_tx(bar[B_V + (c + 1) % NSTF], TILE_A);
-            tma_2d(sA[(c + 1) % NSTF], &mVt, (c + 1) * TJ, bh * 128, bar[B_V + (c + 1) % NSTF]);
+        const int m = c - c0, st = m & 1, j = c * TJ + jl;
+        const bool com_mma = c >= c0 && c < nch;
+        if (com_mma && m >= 2) ok = __all_sync(FULL, ok && espera(bar[B_PV + st], ((m - 2) >> 1) & 1, aborta, kid, 26));      // tile st is free again
+        if (com_mma && m >= 2 && m + 1 >= NSTF && m + 1 < nviv && tid == 0 && ok) {      // and so is the operand stage of chunk m - 2: it takes chunk m + 1
+            mbar_expect_tx(bar[B_V + (m + 1) % NSTF], TILE_A);
+            tma_2d(sA[(m + 1) % NSTF], &mVt, (c + 1) * TJ, bh * 128, bar[B_V + (m + 1) % NSTF]);
         }
         uint32_t w[4] = {0, 0, 0, 0};
-        if (j < nproc) {
+        if (com_mma && j < nproc) {
 #pragma unroll
             for (int k = 0; k < 16; k++) {
                 const int p = min(((int)ex_s[(16 * g + k) * TPX + j] * mi[k] + (1 << 19)) >> 20, 255);
@@ -404,12 +442,12 @@ __global__ void __launch_bounds__(NTL) k_atencao_tc(const __grid_constant__ CUte
         fence_async();                                             // the tile is read by the tensor core (async proxy)
         __syncthreads();
         if (tid == 0 && ok) {
-            ok = espera(bar[B_V + c % NSTF], (c / NSTF) & 1, aborta, kid, 23);
+            ok = espera(bar[B_V + m % NSTF], (m / NSTF) & 1, aborta, kid, 23);
             if (ok) {
                 tc_fence_depois();
-                const uint64_t da = desc_sw128(sA[c % NSTF]), db = desc_sw128(sPB + st * TILE_NI);
+                const uint64_t da = desc_sw128(sA[m % NSTF]), db = desc_sw128(sPB + st * TILE_NI);
 #pragma unroll
-                for (int q = 0; q < 4; q++) tc_mma_i8(tmem + 2 * SB, da + 2 * q, db + 2 * q, ID_PU, (c | q) != 0);
+                for (int q = 0; q < 4; q++) tc_mma_i8(tmem + 2 * SB, da + 2 * q, db + 2 * q, ID_PU, (m | q) != 0);
                 tc_commit(bar[B_PV + st]);
                 if (c == nch - 1) tc_commit(bar[B_O]);
             }
@@ -819,12 +857,13 @@ static int atencao_frente_tc(int blk, const int8_t* qm, const int8_t* qE, int* O
                              int D, int GA, int kid, cudaStream_t st) {
     if (Qm && (blk != 32 || !QE)) return (int)cudaErrorInvalidValue;
     const int BH = Bt * H;
-    const size_t b_em = atc_arredonda((size_t)BH * 16), b_lin = atc_arredonda((size_t)BH * T * 128);
+    // head-maximum exponents [BH][4], then the largest squared row norms of q and k per 128 tokens [BH][2][ceil(T/128)]
+    const size_t b_em = atc_arredonda((size_t)BH * 16 + (size_t)BH * 2 * ((T + 127) / 128) * 4), b_lin = atc_arredonda((size_t)BH * T * 128);
     unsigned char* ws = nullptr;
     if (int r = at_ws(b_em + 3 * b_lin, st, reinterpret_cast<void**>(&ws))) return r;
     int* em = reinterpret_cast<int*>(ws);
     int8_t *Q2 = reinterpret_cast<int8_t*>(ws + b_em), *K2 = Q2 + b_lin, *Vt2 = K2 + b_lin;
-    atc::ArgsPrep Pp = {qm, qE, nullptr, nullptr, {Q2, K2, nullptr, nullptr}, {nullptr, nullptr, Vt2, nullptr}, em, nullptr, T, H, D, GA, blk};
+    atc::ArgsPrep Pp = {qm, qE, nullptr, nullptr, {Q2, K2, nullptr, nullptr}, {nullptr, nullptr, Vt2, nullptr}, em, nullptr, em + 4 * BH, T, H, D, GA, blk};
     lanca_pdl(atc::k_at_prep, dim3(dim3((T + 127) / 128, BH, 3)), dim3(256), 0, st, Pp);
     CUtensorMap mQ, mK, mVt;
     if (!(faz_mapa(&mQ, Q2, BH * T, 128, atc::NI) && faz_mapa(&mK, K2, BH * T, 128, 128) && faz_mapa(&mVt, Vt2, BH * 128, T, 128)))
@@ -851,7 +890,7 @@ static int atencao_tras_tc(int blk, const int8_t* gom, const int8_t* goE, const 
     int8_t *V2 = reinterpret_cast<int8_t*>(ws + b_est), *G2 = V2 + b_lin, *Qt2 = G2 + b_lin, *Kt2 = Qt2 + b_lin, *Gt2 = Kt2 + b_lin;
     int8_t *DSh = Gt2 + b_lin, *DSl = DSh + b_ds;
     cudaError_t c;
-    atc::ArgsPrep Pp = {qm, qE, gom, goE, {nullptr, nullptr, V2, G2}, {Qt2, Kt2, nullptr, Gt2}, em, est, T, H, D, GA, blk};
+    atc::ArgsPrep Pp = {qm, qE, gom, goE, {nullptr, nullptr, V2, G2}, {Qt2, Kt2, nullptr, Gt2}, em, est, nullptr, T, H, D, GA, blk};
     lanca_pdl(atc::k_at_prep, dim3(dim3((T + 127) / 128, BH, 4)), dim3(256), 0, st, Pp);
     CUtensorMap mV, mG, mKt, mQt, mGt, mDh, mDl, mP;
     if (!(faz_mapa(&mV, V2, BH * T, 128, 128) && faz_mapa(&mG, G2, BH * T, 128, atc::NI) && faz_mapa(&mKt, Kt2, BH * 128, T, 128) &&

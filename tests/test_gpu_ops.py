@@ -572,3 +572,25 @@ def test_gemm_abandona_uma_espera_e_o_seguinte_e_exato(amb):
     Y = oc.gemm(X, W)
     torch.cuda.synchronize()
     assert [gu.digest(t) for t in Y] == rec["Y"]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("mmax,esp,T", [(127, 5, 1024), (9, 2, 1024), (2, 0, 768), (40, 12, 512)])
+def test_atencao_pedacos_de_chaves_sem_efeito(amb, mmax, esp, T):
+    """The forward leaves out key chunks its norm bound proves to have P = 0 exactly: large and tiny q, k magnitudes (the bound
+    decides how many chunks stay), several sequence lengths, against the oracle bit for bit (P included), and the backward on
+    that P."""
+    ops, oc, reg = amb
+    ops.define_blk(32)
+    reg.novo_passo(0)
+    Bt, H, D = 1, 2, 128
+    G = casos.Gen(77 + mmax + T, 32)
+    qkv, go = G.bloco(Bt * T, 3 * D, espalha=esp, zera=0.02, mmax=mmax), G.bloco(Bt * T, D, e0=-20, espalha=4)
+    s = spec.Spec(32)
+    o_r, P_r = s.atencao(qkv, Bt, T, H)
+    g_r = s.atencao_back(go, qkv, P_r, Bt, T, H)
+    o_c, P_c = oc.atencao(para_gpu(qkv), Bt, T, H)
+    g_c = oc.atencao_back(para_gpu(go), para_gpu(qkv), P_c, Bt, T, H)
+    torch.cuda.synchronize()
+    compara(f"atencao mmax {mmax} T {T}", [*o_c, P_c], [*o_r, P_r])
+    compara(f"atencao_back mmax {mmax} T {T}", list(g_c), list(g_r))
