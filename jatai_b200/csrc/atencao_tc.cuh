@@ -485,9 +485,34 @@ inline size_t smem_frente_tc(int T) {
     return 1024 + 3 * TILE_A + TILE_Q3 + 2 * TILE_NI + 640 + (ex > os ? ex : os);
 }
 
+// -------------------------------------------------------------------------------------------------- where stored P is zero
+// zm[bh][kt] = bit qt set when P (key-major, [BH*T][T]) has a non-zero among keys 64 kt .. 64 kt + 63 and queries 64 qt .. 64 qt + 63.
+// grid (ceil(T / 64), BH), 256 threads: 4 threads per key row, from the diagonal on (P is zero above it by construction).
+__global__ void __launch_bounds__(256) k_p_mapa(const uint8_t* __restrict__ P, int* __restrict__ zm, int T) {
+    pdl_espera();
+    pdl_solta();
+    __shared__ unsigned ou;
+    const int tid = threadIdx.x, kt = blockIdx.x, bh = blockIdx.y, r = tid >> 2, parte = tid & 3, j = kt * NJ + r;
+    if (tid == 0) ou = 0;
+    __syncthreads();
+    unsigned m = 0;
+    if (j < T) {
+        const uint4* linha = reinterpret_cast<const uint4*>(P + ((size_t)bh * T + j) * T);
+        for (int p = 4 * kt + parte; p < T / 16; p += 4) {          // 16-byte pieces; piece p belongs to query tile p / 4
+            const uint4 v = linha[p];
+            if (v.x | v.y | v.z | v.w) m |= 1u << (p >> 2);
+        }
+    }
+    m = __reduce_or_sync(0xffffffffu, m);
+    if ((tid & 31) == 0 && m) atomicOr(&ou, m);
+    __syncthreads();
+    if (tid == 0) zm[bh * gridDim.x + kt] = (int)ou;
+}
+
 // -------------------------------------------------------------------------------------------------- backward, row tiles
 struct ArgsTrasTC {
     const uint8_t* P; int* Gacc; int16_t* Ge; int* est; int* sl; const int* em;      // em: [BH][4] = q, k, v, dO
+    const int* zm;                                                                    // [BH][ceil(T/64)]: per 64 keys, bit qt = P has a non-zero among queries 64 qt .. 64 qt + 63
     int8_t* DSh; int8_t* DSl;                                                         // [BH*T][T] digits of dS', key-major (transposed)
     int8_t* Gm; int8_t* GE;                                                           // block output [M, 3D] instead of the raw one, or nullptr
     int T, H, D, GA, limite, kid;
@@ -522,7 +547,6 @@ __global__ void __launch_bounds__(NTL) k_ab_linhas_tc(const __grid_constant__ CU
     const int bh = ordem % gridDim.y, b = bh / H, h = bh % H, i0 = (gridDim.x - 1 - ordem / gridDim.y) * NI, linha0 = b * T;
     int* est = A.est + bh * at::N_EST;
     const int nproc = i0 + NI, nch = (nproc + TJ - 1) / TJ;
-    const int nvoltas = FASE == 2 ? 2 * nch : nch;                 // phase 2 sweeps the keys twice
     const uint32_t sG = sbase + OFF_G, sG3 = sbase + OFF_G3, sKt0 = sbase + OFF_KT;          // V stage s at sbase + s * TILE_A, K^T stage s at sKt0 + s * TILE_A
     uint8_t* ds_b = smem + OFF_DS;                                 // [2 stages][hi rows | lo rows][64 x 128]
     // first the operand loads (as soon as their barriers exist), then the small global reads, then tensor memory
@@ -536,14 +560,34 @@ __global__ void __launch_bounds__(NTL) k_ab_linhas_tc(const __grid_constant__ CU
     if (tid == 0) {
         mbar_expect_tx(bar[0], TILE_NI);
         tma_2d(sG, &mG, 0, bh * T + i0, bar[0]);
+    }
+    // Key chunks in which stored P is zero for this query tile and its two neighbours (A.zm: per 64 keys, the 64-query tiles
+    // with a non-zero P) add nothing to s_lin, dS' and gq, and the key-tile kernel does not read their dS': phases 2 and 3 leave
+    // them out.  The diagonal chunk always stays; phase 1 (a maximum over every position) and the bounded variant keep them all.
+    unsigned vivos = (1u << nch) - 1u;
+    if (FASE != 1 && !A.limite) {
+        const int qt = i0 / NI, nkt = (T + NJ - 1) / NJ;
+        const unsigned vizinhos = (7u << qt) >> 1;                 // query tiles qt - 1, qt, qt + 1
+        vivos = 1u << (nch - 1);
+        if (qt >= 1) vivos |= 1u << ((qt - 1) / 2);               // the chunk of key tile qt - 1: the key-tile kernel's first step reads it
+        for (int c = 0; c < nch - 1; c++) {
+            unsigned m = (unsigned)A.zm[bh * nkt + 2 * c];
+            if (2 * c + 1 < nkt) m |= (unsigned)A.zm[bh * nkt + 2 * c + 1];
+            if (m & vizinhos) vivos |= 1u << c;
+        }
+    }
+    const int nviv = __popc(vivos);
+    const int nvoltas = FASE == 2 ? 2 * nviv : nviv;               // phase 2 sweeps the keys twice
+    auto pedaco = [&](int cc) -> int { return (int)__fns(vivos, 0, cc % nviv + 1); };      // the live chunk of step cc
+    if (tid == 0) {
         for (int c = 0; c < NSTV && c < nvoltas; c++) {
             mbar_expect_tx(bar[B_V + c], TILE_A);
-            tma_2d(sbase + c * TILE_A, &mV, 0, bh * T + (c % nch) * TJ, bar[B_V + c]);
+            tma_2d(sbase + c * TILE_A, &mV, 0, bh * T + pedaco(c) * TJ, bar[B_V + c]);
         }
         if (FASE == 3)
-            for (int c = 0; c < 2 && c < nch; c++) {
+            for (int c = 0; c < 2 && c < nviv; c++) {
                 mbar_expect_tx(bar[B_KT + c], TILE_A);
-                tma_2d(sKt0 + c * TILE_A, &mKt, c * TJ, bh * 128, bar[B_KT + c]);
+                tma_2d(sKt0 + c * TILE_A, &mKt, pedaco(c) * TJ, bh * 128, bar[B_KT + c]);
             }
     }
     const int emk = A.em[bh * 4 + 1], emv = A.em[bh * 4 + 2], emg = A.em[bh * 4 + 3];
@@ -573,25 +617,25 @@ __global__ void __launch_bounds__(NTL) k_ab_linhas_tc(const __grid_constant__ CU
     __syncthreads();
     if (tid == 0 && ok) ok = emite(0);
     for (int cc = 0; cc < nvoltas; cc++) {
-        const int c = cc % nch, st = cc & 1;
+        const int c = pedaco(cc), st = cc & 1;
         if (tid == 0 && ok && cc + 1 < nvoltas) ok = emite(cc + 1);
         __syncwarp();
         ok = __all_sync(FULL, ok && espera(bar[B_S + st], (cc >> 1) & 1, aborta, kid, 32));
         tc_fence_depois();
         if (tid == 0 && ok && cc + NSTV < nvoltas) {               // this step's MMAs are done: its stage takes the chunk of step cc + 4
             mbar_expect_tx(bar[B_V + cc % NSTV], TILE_A);
-            tma_2d(sbase + (cc % NSTV) * TILE_A, &mV, 0, bh * T + ((cc + NSTV) % nch) * TJ, bar[B_V + cc % NSTV]);
+            tma_2d(sbase + (cc % NSTV) * TILE_A, &mV, 0, bh * T + pedaco(cc + NSTV) * TJ, bar[B_V + cc % NSTV]);
         }
         if (FASE == 3) {
             // the digit tiles of this parity and the K^T stage of chunk cc - 2 are free once that chunk's output MMAs are done;
             // the stage takes chunk cc + 2 (the first two steps fill the stages nobody has used yet)
             if (cc >= 2) ok = __all_sync(FULL, ok && espera(bar[B_G + st], ((cc - 2) >> 1) & 1, aborta, kid, 33));
-            if (tid == 0 && ok && cc + 2 < nch) {
+            if (tid == 0 && ok && cc + 2 < nviv) {
                 mbar_expect_tx(bar[B_KT + (cc + 2) % NSTV], TILE_A);
-                tma_2d(sKt0 + ((cc + 2) % NSTV) * TILE_A, &mKt, (cc + 2) * TJ, bh * 128, bar[B_KT + (cc + 2) % NSTV]);
+                tma_2d(sKt0 + ((cc + 2) % NSTV) * TILE_A, &mKt, pedaco(cc + 2) * TJ, bh * 128, bar[B_KT + (cc + 2) % NSTV]);
             }
         }
-        if (FASE == 2 && cc == nch) {
+        if (FASE == 2 && cc == nviv) {
             // between the sweeps: s_lin of the 32 rows from the per-thread partial sums
 #pragma unroll
             for (int k = 0; k < 16; k++) {
@@ -632,11 +676,11 @@ __global__ void __launch_bounds__(NTL) k_ab_linhas_tc(const __grid_constant__ CU
                     else if (RAP) gp = (x + meio1 + ((x >> sh) & 1)) >> sh;
                     else gp = rnd_d(x, sh);
                     gp = dentro ? gp : 0;
-                    if (FASE == 1 || (FASE == 2 && cc < nch)) mgp = max(mgp, gp < 0 ? -gp : gp);
+                    if (FASE == 1 || (FASE == 2 && cc < nviv)) mgp = max(mgp, gp < 0 ? -gp : gp);
                     if (FASE == 1) continue;
                     const int p = (int)((pw[k >> 2] >> (8 * (k & 3))) & 0xff);
                     if (FASE == 2) {
-                        if (cc < nch) s_part[k] += p * gp;
+                        if (cc < nviv) s_part[k] += p * gp;
                         else {
                             const int ds = p * (gp - sl_s[16 * g + k]);
                             mds = max(mds, ds < 0 ? -ds : ds);
@@ -753,8 +797,8 @@ __global__ void __launch_bounds__(256) k_ab_colunas_tc(const __grid_constant__ C
     const int bh = ordem % gridDim.y, b = bh / H, h = bh % H, j0 = (ordem / gridDim.y) * NJ, linha0 = b * T;
     const int* est = A.est + bh * at::N_EST;
     const int nq = (T - j0 + TJ - 1) / TJ;
-    auto carrega = [&](int c) {                                    // one thread: the five operand tiles of query chunk c
-        const uint32_t s = sbase + (c % NSTC) * STAGE, f = bar[c % NSTC];
+    auto carrega = [&](int n, int c) {                             // one thread: the five operand tiles of query chunk c, step n
+        const uint32_t s = sbase + (n % NSTC) * STAGE, f = bar[n % NSTC];
         const int ic = j0 + c * TJ;
         mbar_expect_tx(f, STAGE);
         tma_2d(s, &mQt, ic, bh * 128, f);
@@ -770,8 +814,19 @@ __global__ void __launch_bounds__(256) k_ab_colunas_tc(const __grid_constant__ C
     }
     pdl_espera();                                                  // the operands are the previous kernels' outputs
     pdl_solta();
+    // query chunks (128 queries from j0 + 128 c) in which stored P is zero for this key tile add nothing to gk and gv, and phase 3
+    // wrote no dS' there: they are left out.  The first step (the diagonal) always stays.
+    unsigned vivos = (1u << nq) - 1u;
+    if (!A.limite) {
+        const unsigned m = (unsigned)A.zm[bh * ((T + NJ - 1) / NJ) + j0 / NJ];
+        vivos = 1u;
+        for (int c = 1; c < nq; c++)
+            if (m & (3u << ((j0 + c * TJ) / NI))) vivos |= 1u << c;
+    }
+    const int nviv = __popc(vivos);
+    auto passo = [&](int n) -> int { return (int)__fns(vivos, 0, n + 1); };      // the query chunk of live step n
     if (tid == 0)                                                  // the loads go out before anything else
-        for (int c = 0; c < NSTC && c < nq; c++) carrega(c);
+        for (int n = 0; n < NSTC && n < nviv; n++) carrega(n, passo(n));
     if (wid == 0) tmem_aloca(slot, 256);
     tc_fence_antes();
     __syncthreads();
@@ -779,7 +834,7 @@ __global__ void __launch_bounds__(256) k_ab_colunas_tc(const __grid_constant__ C
     const uint32_t tmem = *slot;
     if (tid == 0) {
         bool ok = true;
-        for (int c = 0; c < nq && ok; c++) {
+        for (int c = 0; c < nviv && ok; c++) {                      // c counts the live steps
             ok = espera(bar[c % NSTC], (c / NSTC) & 1, aborta, kid, 40);
             if (!ok) break;
             tc_fence_depois();
@@ -792,9 +847,9 @@ __global__ void __launch_bounds__(256) k_ab_colunas_tc(const __grid_constant__ C
                 tc_mma_i8(tmem + 128, dg + 2 * q, dp + 2 * q, ID_CU, (c | q) != 0);
             }
             tc_commit(bar[NSTC + c % NSTC]);
-            if (c >= 1 && c + 2 < nq) {                            // chunk c - 1's MMAs done: its stage takes chunk c + 2
+            if (c >= 1 && c + 2 < nviv) {                          // step c - 1's MMAs done: its stage takes step c + 2
                 ok = espera(bar[NSTC + (c - 1) % NSTC], ((c - 1) / NSTC) & 1, aborta, kid, 41);
-                if (ok) carrega(c + 2);
+                if (ok) carrega(c + 2, passo(c + 2));
             }
         }
         tc_commit(bar[2 * NSTC]);
@@ -880,13 +935,14 @@ static int atencao_tras_tc(int blk, const int8_t* gom, const int8_t* goE, const 
                            int8_t* Gm, int8_t* GE, int Bt, int T, int H, int D, int GA, int limite, int kid, cudaStream_t st) {
     if (Gm && (blk != 32 || !GE)) return (int)cudaErrorInvalidValue;
     const int BH = Bt * H;
-    const size_t b_est = atc_arredonda((size_t)BH * (at::N_EST + T + 4) * sizeof(int)), b_lin = atc_arredonda((size_t)BH * T * 128),
+    const size_t b_est = atc_arredonda((size_t)BH * (at::N_EST + T + 4 + 16) * sizeof(int)), b_lin = atc_arredonda((size_t)BH * T * 128),
                  b_ds = atc_arredonda((size_t)BH * T * T);
     unsigned char* ws = nullptr;
     if (int r = at_ws(b_est + 5 * b_lin + 2 * b_ds, st, reinterpret_cast<void**>(&ws))) return r;
     int* est = reinterpret_cast<int*>(ws);
     int* sl = est + (size_t)BH * at::N_EST;
     int* em = sl + (size_t)BH * T;
+    int* zm = em + (size_t)BH * 4;                               // [BH][ceil(T/64)] (T <= 1024: at most 16 per head)
     int8_t *V2 = reinterpret_cast<int8_t*>(ws + b_est), *G2 = V2 + b_lin, *Qt2 = G2 + b_lin, *Kt2 = Qt2 + b_lin, *Gt2 = Kt2 + b_lin;
     int8_t *DSh = Gt2 + b_lin, *DSl = DSh + b_ds;
     cudaError_t c;
@@ -897,7 +953,8 @@ static int atencao_tras_tc(int blk, const int8_t* gom, const int8_t* goE, const 
           faz_mapa(&mQt, Qt2, BH * 128, T, 128) && faz_mapa(&mGt, Gt2, BH * 128, T, 128) && faz_mapa(&mDh, DSh, BH * T, T, atc::NJ) &&
           faz_mapa(&mDl, DSl, BH * T, T, atc::NJ) && faz_mapa(&mP, P, BH * T, T, atc::NJ)))
         return (int)cudaErrorInvalidValue;
-    atc::ArgsTrasTC A = {P, Gacc, Ge, est, sl, em, DSh, DSl, Gm, GE, T, H, D, GA, limite, kid};
+    atc::ArgsTrasTC A = {P, Gacc, Ge, est, sl, em, zm, DSh, DSl, Gm, GE, T, H, D, GA, limite, kid};
+    if (!limite) lanca_pdl(atc::k_p_mapa, dim3((T + atc::NJ - 1) / atc::NJ, BH), dim3(256), 0, st, P, zm, T);
     const dim3 grade(T / atc::NI, BH);
     if (limite) {
         at::ArgsTras L = {gom, goE, qm, qE, P, Gacc, Ge, est, sl, nullptr, T, H, D, GA, blk, limite, kid};
