@@ -594,3 +594,26 @@ def test_atencao_pedacos_de_chaves_sem_efeito(amb, mmax, esp, T):
     torch.cuda.synchronize()
     compara(f"atencao mmax {mmax} T {T}", [*o_c, P_c], [*o_r, P_r])
     compara(f"atencao_back mmax {mmax} T {T}", list(g_c), list(g_r))
+
+
+@pytest.mark.gpu
+def test_atencao_back_com_P_alterado(amb):
+    """The backward works from the P it is given: with whole tiles of P zeroed by hand (tiles its zero map then leaves out, tiles
+    next to the diagonal, a whole key range) it still equals the oracle's backward on that same P."""
+    ops, oc, reg = amb
+    ops.define_blk(32)
+    reg.novo_passo(0)
+    Bt, T, H, D = 1, 1024, 2, 128
+    G = casos.Gen(4242, 32)
+    qkv, go = G.bloco(Bt * T, 3 * D, espalha=3, zera=0.02, mmax=30), G.bloco(Bt * T, D, e0=-20, espalha=4)
+    s = spec.Spec(32)
+    _, P = s.atencao(qkv, Bt, T, H)
+    P = P.clone()                                    # [Bt*H, T (keys), T (queries)]
+    P[0, 0:128, 256:] = 0                            # a far key range for all later queries
+    P[0, 512:576, 576:640] = 0                       # the tile right of a diagonal tile
+    P[1, 640:704, 640:704] = 0                       # a diagonal tile itself
+    P[1, :, 896:960] = 0                             # every key of one query tile
+    g_r = s.atencao_back(go, qkv, P, Bt, T, H)
+    g_c = oc.atencao_back(para_gpu(go), para_gpu(qkv), para_gpu(P), Bt, T, H)
+    torch.cuda.synchronize()
+    compara("atencao_back with hand-zeroed tiles of P", list(g_c), list(g_r))
