@@ -477,13 +477,13 @@ def mede_sweep(oc, reg, dev, reps=3):
 def nucleos_por_passo(reg, c):
     """Kernels of this library launched per step: one per recorded operation, except the attention on the tensor-core
     path (head dimension 64, T >= 128), whose forward is 2 launches (operand preparation + the kernel) and whose backward is
-    6 (preparation, the map of zero tiles of P, three row phases, the key-tile kernel).  The split-K memsets are not counted."""
+    5 (preparation, three row phases, the key-tile kernel), 6 with the map of zero tiles of P from T = 512 on.  The split-K memsets are not counted."""
     from jatai_b200 import ops
     n = len(reg.lancamentos)
     if ops.BLK == 32 and c["D"] == 64 * c["H"] and c["T"] % 64 == 0 and 128 <= c["T"] <= 1024:
         for lanc in reg.lancamentos:
             if lanc["op"].startswith("atencao_back"):
-                n += 4 if ops.ATENCAO_LIMITE else 5
+                n += 4 if (ops.ATENCAO_LIMITE or c["T"] <= 256) else 5
             elif lanc["op"].startswith("atencao"):
                 n += 1
     return n

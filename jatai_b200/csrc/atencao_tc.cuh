@@ -271,9 +271,15 @@ __global__ void __launch_bounds__(NTL) k_atencao_tc(const __grid_constant__ CUte
     }
     pdl_espera();                                                  // the operands below are the previous kernel's outputs
     pdl_solta();
+    const bool pode_pular = T > 2 * TJ;                            // up to two key chunks nearly every chunk is next to the diagonal
     if (tid == 0) {
         mbar_expect_tx(bar[0], TILE_NI);
         tma_2d(sQ, &mQ, 0, bh * T + i0, bar[0]);
+        if (!pode_pular)                                           // every chunk stays: its loads need not wait for the bound
+            for (int c = 0; c < NSTF && c < 2 * nch; c++) {
+                mbar_expect_tx(bar[B_K + c], TILE_A);
+                tma_2d(sA[c], &mK, 0, bh * T + (c % nch) * TJ, bar[B_K + c]);
+            }
     }
     const int emq = em[bh * 4], emk = em[bh * 4 + 1], emv = em[bh * 4 + 2];
     const int s_u = -((emq - GA) + (emk - GA) - 3 + 8), incl = at::incl_alibi(h);
@@ -283,7 +289,7 @@ __global__ void __launch_bounds__(NTL) k_atencao_tc(const __grid_constant__ CUte
     // (i - j) 2^incl >= 2132 + 2 B adds nothing to the row sum, cannot be the maximum and has P = 0: chunks wholly at that distance
     // from the tile's first query are left out of all three passes (P = 0 is still written).  Only on the right-shift path.
     int c0 = 0;
-    if (s_u > 0 && s_u < 31) {
+    if (pode_pular && s_u > 0 && s_u < 31) {
         const int* nrm = em + 4 * gridDim.y;
         const int nq = nrm[((size_t)bh * 2) * nchT + i0 / TJ];
         int nk = 0;
@@ -293,7 +299,7 @@ __global__ void __launch_bounds__(NTL) k_atencao_tc(const __grid_constant__ CUte
         if (i0 - D0 + 1 > 0) c0 = (int)((i0 - D0 + 1) / TJ);
     }
     const int nviv = nch - c0, nvoltas = 2 * nviv;                  // live chunks c0 .. nch - 1, swept twice
-    if (tid == 0) {
+    if (tid == 0 && pode_pular) {
         for (int c = 0; c < NSTF && c < nvoltas; c++) {
             mbar_expect_tx(bar[B_K + c], TILE_A);
             tma_2d(sA[c], &mK, 0, bh * T + (c0 + c % nviv) * TJ, bar[B_K + c]);
@@ -565,7 +571,7 @@ __global__ void __launch_bounds__(NTL) k_ab_linhas_tc(const __grid_constant__ CU
     // with a non-zero P) add nothing to s_lin, dS' and gq, and the key-tile kernel does not read their dS': phases 2 and 3 leave
     // them out.  The diagonal chunk always stays; phase 1 (a maximum over every position) and the bounded variant keep them all.
     unsigned vivos = (1u << nch) - 1u;
-    if (FASE != 1 && !A.limite) {
+    if (FASE != 1 && !A.limite && A.zm) {
         const int qt = i0 / NI, nkt = (T + NJ - 1) / NJ;
         const unsigned vizinhos = (7u << qt) >> 1;                 // query tiles qt - 1, qt, qt + 1
         vivos = 1u << (nch - 1);
@@ -817,7 +823,7 @@ __global__ void __launch_bounds__(256) k_ab_colunas_tc(const __grid_constant__ C
     // query chunks (128 queries from j0 + 128 c) in which stored P is zero for this key tile add nothing to gk and gv, and phase 3
     // wrote no dS' there: they are left out.  The first step (the diagonal) always stays.
     unsigned vivos = (1u << nq) - 1u;
-    if (!A.limite) {
+    if (!A.limite && A.zm) {
         const unsigned m = (unsigned)A.zm[bh * ((T + NJ - 1) / NJ) + j0 / NJ];
         vivos = 1u;
         for (int c = 1; c < nq; c++)
@@ -918,7 +924,7 @@ static int atencao_frente_tc(int blk, const int8_t* qm, const int8_t* qE, int* O
     if (int r = at_ws(b_em + 3 * b_lin, st, reinterpret_cast<void**>(&ws))) return r;
     int* em = reinterpret_cast<int*>(ws);
     int8_t *Q2 = reinterpret_cast<int8_t*>(ws + b_em), *K2 = Q2 + b_lin, *Vt2 = K2 + b_lin;
-    atc::ArgsPrep Pp = {qm, qE, nullptr, nullptr, {Q2, K2, nullptr, nullptr}, {nullptr, nullptr, Vt2, nullptr}, em, nullptr, em + 4 * BH, T, H, D, GA, blk};
+    atc::ArgsPrep Pp = {qm, qE, nullptr, nullptr, {Q2, K2, nullptr, nullptr}, {nullptr, nullptr, Vt2, nullptr}, em, nullptr, T > 2 * atc::TJ ? em + 4 * BH : nullptr, T, H, D, GA, blk};
     lanca_pdl(atc::k_at_prep, dim3(dim3((T + 127) / 128, BH, 3)), dim3(256), 0, st, Pp);
     CUtensorMap mQ, mK, mVt;
     if (!(faz_mapa(&mQ, Q2, BH * T, 128, atc::NI) && faz_mapa(&mK, K2, BH * T, 128, 128) && faz_mapa(&mVt, Vt2, BH * 128, T, 128)))
@@ -953,8 +959,10 @@ static int atencao_tras_tc(int blk, const int8_t* gom, const int8_t* goE, const 
           faz_mapa(&mQt, Qt2, BH * 128, T, 128) && faz_mapa(&mGt, Gt2, BH * 128, T, 128) && faz_mapa(&mDh, DSh, BH * T, T, atc::NJ) &&
           faz_mapa(&mDl, DSl, BH * T, T, atc::NJ) && faz_mapa(&mP, P, BH * T, T, atc::NJ)))
         return (int)cudaErrorInvalidValue;
-    atc::ArgsTrasTC A = {P, Gacc, Ge, est, sl, em, zm, DSh, DSl, Gm, GE, T, H, D, GA, limite, kid};
-    if (!limite) lanca_pdl(atc::k_p_mapa, dim3((T + atc::NJ - 1) / atc::NJ, BH), dim3(256), 0, st, P, zm, T);
+    // the map of zero tiles of P pays from three key chunks on (T > 256): below that nearly every chunk is next to the diagonal
+    const bool com_mapa = !limite && T > 256;
+    atc::ArgsTrasTC A = {P, Gacc, Ge, est, sl, em, com_mapa ? zm : nullptr, DSh, DSl, Gm, GE, T, H, D, GA, limite, kid};
+    if (com_mapa) lanca_pdl(atc::k_p_mapa, dim3((T + atc::NJ - 1) / atc::NJ, BH), dim3(256), 0, st, P, zm, T);
     const dim3 grade(T / atc::NI, BH);
     if (limite) {
         at::ArgsTras L = {gom, goE, qm, qE, P, Gacc, Ge, est, sl, nullptr, T, H, D, GA, blk, limite, kid};
