@@ -120,11 +120,11 @@ class Modelo:
         backward, between the two collectives of the step (see `_gemms_adiados`)."""
         ops = self.ops
         if self._lado is None:
-            a, b = self._transpoe_par(gy, x)
             if self.redutor is None:
+                a, b = self._transpoe_par(gy, x)
                 self._grads[nome] = ops.gemm(a, b, cru=True)
             else:
-                self._adiados.append((nome, a, b, ops.max_linha(a), ops.max_linha(b)))
+                self._adiados.append((nome, *self._transpoe_par_max(gy, x)))
             return
         # A weight gradient is a leaf of the backward graph: its two transpositions and its GEMM run on a second
         # stream, next to the dX chain, and fill SMs the small GEMMs of that chain leave idle.  Under capture the
